@@ -1,0 +1,143 @@
+/*
+ * sage3_b200.h -- C ABI of libsage3_b200.so: SageAttention3 (NVFP4 attention) for NVIDIA B200 (sm_100a).
+ *
+ * Plain pointers and sizes only; no framework types cross this boundary.  Every buffer, including the
+ * workspace, is allocated by the caller and must be device memory of the current CUDA device.  All
+ * work is enqueued on the caller's stream; the functions return as soon as the launches are queued.
+ * Functions return 0 on success and a negative SAGE3_E_* code otherwise (see sage3_strerror); they
+ * never throw and never terminate the process.
+ *
+ * The entry points replace the two pybind11 modules of the reference
+ * (paths inside the reference project, sageattention3_blackwell/sageattn3/...):
+ *   fp4quant_cuda.scaled_fp4_quant / _permute / _trans   quantization/fp4_quantization_4d.cu:388-628
+ *   fp4attn_cuda.fwd                                     blackwell/api.cu:203-341
+ * and the Python pre-processing in front of them (api.py:75-92, preprocess_qkv).
+ */
+#ifndef SAGE3_B200_H_
+#define SAGE3_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SAGE3_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define SAGE3_API __attribute__((visibility("default")))
+#else
+#define SAGE3_API
+#endif
+
+enum {
+    SAGE3_OK = 0,
+    SAGE3_E_NULL = -1,        /* a required pointer is NULL */
+    SAGE3_E_SHAPE = -2,       /* unsupported shape: D not in {64,128}, Hq % Hkv != 0, sizes <= 0 ... */
+    SAGE3_E_DTYPE = -3,       /* dtype is neither SAGE3_FP16 nor SAGE3_BF16 */
+    SAGE3_E_STRIDE = -4,      /* a stride breaks the 16-byte alignment the vector loads need */
+    SAGE3_E_ALIGN = -5,       /* a base pointer is not 16-byte (workspace: 256-byte) aligned */
+    SAGE3_E_ARCH = -6,        /* the current device is not compute capability 10.0 */
+    SAGE3_E_CUDA = -7,        /* a CUDA runtime / driver call or a kernel launch failed */
+    SAGE3_E_TOO_LARGE = -8,   /* a size exceeds a fixed limit of the entry point */
+    SAGE3_E_DEVICE_WAIT = -9  /* (sage3_check_status) a bounded device-side wait gave up */
+};
+
+enum { SAGE3_FP16 = 0, SAGE3_BF16 = 1 };
+
+/*
+ * Problem description.  Tensors are addressed as x[b][h][n][d] with the element strides given here and
+ * d contiguous, so "HND" ([B,H,N,D]) and "NHD" ([B,N,H,D]) callers use the same code path
+ * (the keyword surface of sageattention/core.py:79-157 `tensor_layout`).
+ * GQA: query head h reads kv head h / (Hq / Hkv).  Causal masks are bottom-right aligned
+ * (key j is visible to query i iff j <= i + Nk - Nq), as in blackwell/mainloop_tma_ws.h:286-289.
+ */
+typedef struct Sage3Desc {
+    int32_t B, Hq, Hkv, Nq, Nk, D;
+    int32_t dtype;            /* SAGE3_FP16 | SAGE3_BF16: element type of q, k, v and out */
+    int32_t is_causal;
+    int32_t per_block_mean;   /* 1: Q smoothed per 128-row block (api.py:86-87); 0: one mean per head (api.py:88-90) */
+    int32_t reserved;
+    int64_t q_stride[3];      /* element strides of q for (b, h, n) */
+    int64_t k_stride[3];
+    int64_t v_stride[3];
+    int64_t o_stride[3];
+    float sm_scale;           /* softmax scale; <= 0 selects D^-0.5 (api.py:127) */
+    int32_t reserved2;
+    const float* sm_scale_per_head;   /* optional device array [Hq] overriding sm_scale; NULL if unused */
+} Sage3Desc;
+
+/*
+ * Byte offsets of the regions inside the workspace (all multiples of 1024).  Np = N rounded up to 128.
+ *   status   int32[64]                        device-written status words (0 = fine)
+ *   kpart    fp32 [B*Hkv][chunks][D]          scratch: partial column sums of K (and of Q when per_block_mean = 0)
+ *   km       dtype[B][Hkv][D]                 mean of K over its Nk tokens
+ *   qm       dtype[B][Hq][nqm][D]             Q means; nqm = Nq_p/128, or 1 when per_block_mean = 0
+ *   delta    dtype[B][Hq][nqm][Nk_p]          qm . k'^T  (api.py:91)
+ *   q_codes  u8   [B][Hq][Nq_p][D/2]          E2M1, element 2i in bits 0-3 of byte i
+ *   q_sf     u8   [B][Hq][Nq_p/128][D/64][512]   E4M3 scales in 128-row x 4-scale atoms:
+ *                                              byte (r % 32) * 16 + (r / 32) * 4 + (c % 4), atom index c / 4
+ *   k_codes, k_sf                             same for K (kv heads), natural token order
+ *   v_codes  u8   [B][Hkv][D][Nk_p/2]         V transposed, microblocks of 16 consecutive tokens
+ *   v_sf     u8   [B][Hkv][Nk_p/128][2][512]  atoms with r = channel, c = (token % 128) / 16
+ */
+typedef struct Sage3Workspace {
+    size_t status, kpart, km, qm, delta, q_codes, q_sf, k_codes, k_sf, v_codes, v_sf;
+    size_t total_bytes;
+    int32_t nq_pad, nk_pad, nqm, kchunks;
+} Sage3Workspace;
+
+/* ABI version of the loaded library (SAGE3_ABI_VERSION at build time). */
+SAGE3_API int sage3_version(void);
+
+/* Static, never-NULL text for a status code. */
+SAGE3_API const char* sage3_strerror(int code);
+
+/* Validates `desc` and fills `ws` with the workspace layout.  No device work.
+ * Replaces the shape arithmetic of api.py:94-116 and the checks of blackwell/api.cu:219-286. */
+SAGE3_API int sage3_workspace_layout(const Sage3Desc* desc, Sage3Workspace* ws);
+
+/* Bytes of workspace `desc` needs (0 if desc is invalid). */
+SAGE3_API size_t sage3_workspace_bytes(const Sage3Desc* desc);
+
+/*
+ * Pre-pass: K smoothing, Q smoothing, delta_s, and NVFP4 quantization of Q, K and V-transposed into
+ * `ws`.  Never writes to q, k or v (the reference smooths K in place, api.py:84).
+ * Replaces preprocess_qkv (api.py:75-92) + scale_and_quant_fp4 / _permute / _transpose (api.py:94-116)
+ * and the kernels behind them (fp4_quantization_4d.cu:133-386).
+ * `stream` is a cudaStream_t.
+ */
+SAGE3_API int sage3_prepass(const Sage3Desc* desc, const void* q, const void* k, const void* v, void* ws, void* stream);
+
+/*
+ * Attention over a workspace filled by sage3_prepass with the same `desc`: out[b][h][n][d] in `dtype`
+ * with the strides of desc->o_stride.  Replaces fp4attn_cuda.fwd (blackwell/api.cu:203-341) and the
+ * final slice of api.py:151 (rows beyond Nq are never written).
+ * `lse` is reserved for a natural-log log-sum-exp output [B][Hq][Nq] and must be NULL for now.
+ */
+SAGE3_API int sage3_attn_fwd(const Sage3Desc* desc, void* ws, void* out, float* lse, void* stream);
+
+/* sage3_prepass followed by sage3_attn_fwd on the same stream. */
+SAGE3_API int sage3_fwd(const Sage3Desc* desc, const void* q, const void* k, const void* v, void* ws, void* out,
+              float* lse, void* stream);
+
+/*
+ * Synchronizes `stream`, reads the status words of `ws` back and returns SAGE3_OK or
+ * SAGE3_E_DEVICE_WAIT; the first non-zero word is stored in *word when word != NULL.
+ * Debugging aid: device-side waits are bounded and report here instead of hanging.
+ */
+SAGE3_API int sage3_check_status(const void* ws, int32_t* word, void* stream);
+
+/*
+ * Diagnostics variant of sage3_attn_fwd: additionally dumps, for the first query tile of the first
+ * (batch, head), the scores of the first processed KV block, its row maxima / partial sums, the final
+ * row sums and the unnormalized output accumulators into `debug` (device, 33280 floats).
+ * No counterpart in the reference.
+ */
+SAGE3_API int sage3_attn_fwd_debug(const Sage3Desc* desc, void* ws, void* out, float* debug, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SAGE3_B200_H_ */

@@ -1,0 +1,8 @@
+"""sageattention_b200 -- SageAttention3 (NVFP4 attention) for NVIDIA B200, hand-written sm_100a CUDA behind a C ABI.
+
+Public surface (mirrors the reference's): sageattn3, sageattn3_blackwell, sageattn.
+"""
+from .api import Sage3Problem, sageattn, sageattn3, sageattn3_blackwell
+
+__all__ = ["sageattn3", "sageattn3_blackwell", "sageattn", "Sage3Problem"]
+__version__ = "0.1.0"

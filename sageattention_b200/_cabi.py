@@ -1,0 +1,83 @@
+"""ctypes binding of libsage3_b200.so (the C ABI declared in include/sage3_b200.h).
+
+The library must have been built (python -m sageattention_b200.build); there is no fallback: if it is
+missing, importing this module raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import pathlib
+
+_PKG = pathlib.Path(__file__).resolve().parent
+LIB_PATH = _PKG / "libsage3_b200.so"
+
+SAGE3_FP16, SAGE3_BF16 = 0, 1
+SAGE3_OK = 0
+SAGE3_E_DEVICE_WAIT = -9
+DEBUG_FLOATS = 33280
+
+
+class Sage3Desc(C.Structure):
+    _fields_ = [
+        ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("Nq", C.c_int32), ("Nk", C.c_int32), ("D", C.c_int32),
+        ("dtype", C.c_int32), ("is_causal", C.c_int32), ("per_block_mean", C.c_int32), ("reserved", C.c_int32),
+        ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3), ("v_stride", C.c_int64 * 3), ("o_stride", C.c_int64 * 3),
+        ("sm_scale", C.c_float), ("reserved2", C.c_int32), ("sm_scale_per_head", C.c_void_p),
+    ]
+
+
+class Sage3Workspace(C.Structure):
+    _fields_ = [(n, C.c_size_t) for n in
+                ("status", "kpart", "km", "qm", "delta", "q_codes", "q_sf", "k_codes", "k_sf", "v_codes", "v_sf",
+                 "total_bytes")] + [(n, C.c_int32) for n in ("nq_pad", "nk_pad", "nqm", "kchunks")]
+
+
+class Sage3Error(RuntimeError):
+    def __init__(self, code: int, where: str):
+        self.code = code
+        super().__init__(f"{where}: {lib().sage3_strerror(code).decode()} (code {code})")
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Loads the shared library once.  Raises if it has not been built: there is no CPU or eager path."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing; build it with `python -m sageattention_b200.build` "
+            "(needs nvcc with sm_100a support). sageattention_b200 has no fallback path.")
+    l = C.CDLL(str(LIB_PATH))
+    P, V = C.POINTER, C.c_void_p
+    l.sage3_version.restype = C.c_int
+    l.sage3_version.argtypes = []
+    l.sage3_strerror.restype = C.c_char_p
+    l.sage3_strerror.argtypes = [C.c_int]
+    l.sage3_workspace_layout.restype = C.c_int
+    l.sage3_workspace_layout.argtypes = [P(Sage3Desc), P(Sage3Workspace)]
+    l.sage3_workspace_bytes.restype = C.c_size_t
+    l.sage3_workspace_bytes.argtypes = [P(Sage3Desc)]
+    l.sage3_prepass.restype = C.c_int
+    l.sage3_prepass.argtypes = [P(Sage3Desc), V, V, V, V, V]
+    l.sage3_attn_fwd.restype = C.c_int
+    l.sage3_attn_fwd.argtypes = [P(Sage3Desc), V, V, V, V]
+    l.sage3_attn_fwd_debug.restype = C.c_int
+    l.sage3_attn_fwd_debug.argtypes = [P(Sage3Desc), V, V, V, V]
+    l.sage3_fwd.restype = C.c_int
+    l.sage3_fwd.argtypes = [P(Sage3Desc), V, V, V, V, V, V, V]
+    l.sage3_check_status.restype = C.c_int
+    l.sage3_check_status.argtypes = [V, P(C.c_int32), V]
+    _lib = l
+    return l
+
+
+EXPORTED = ["sage3_version", "sage3_strerror", "sage3_workspace_layout", "sage3_workspace_bytes", "sage3_prepass",
+            "sage3_attn_fwd", "sage3_fwd", "sage3_check_status", "sage3_attn_fwd_debug"]
+
+
+def check(code: int, where: str) -> None:
+    if code != SAGE3_OK:
+        raise Sage3Error(code, where)

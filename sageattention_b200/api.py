@@ -1,0 +1,188 @@
+"""Host-side mirror of the reference's Python call surface, in front of the sm_100a C-ABI library.
+
+Keeps the keyword surface of
+  sageattn3_blackwell(q, k, v, attn_mask=None, is_causal=False, per_block_mean=True, **kwargs)
+      (reference: sageattention3_blackwell/sageattn3/api.py:131-152)
+  sageattn(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, return_lse=False, **kwargs)
+      (reference: sageattention/core.py:79-157)
+so the function can be patched over F.scaled_dot_product_attention or called from an attention
+processor exactly like the reference's.  Differences, all deliberate:
+  * inputs are never modified (the reference smooths k in place, api.py:84);
+  * no fallback: an unsupported head dim, device or a missing library raises (the reference falls back to
+    torch SDPA for D >= 256, api.py:132-134, and the v2 dispatcher raises on sm_100, core.py:156-157);
+  * attn_mask other than None raises (the reference ignores it silently);
+  * GQA (Hq a multiple of Hkv), Nq != Nk, "NHD" layout and a per-head sm_scale tensor are accepted.
+PyTorch is used for device memory and the current stream only.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from . import _cabi
+
+_DTYPES = {torch.float16: _cabi.SAGE3_FP16, torch.bfloat16: _cabi.SAGE3_BF16}
+
+
+def _bhn_strides(x: torch.Tensor, tensor_layout: str) -> tuple[int, int, int]:
+    s = x.stride()
+    return (s[0], s[1], s[2]) if tensor_layout == "HND" else (s[0], s[2], s[1])
+
+
+def _usable(x: torch.Tensor) -> bool:
+    return x.stride(-1) == 1 and all(st % 8 == 0 for st in x.stride()[:-1]) and x.data_ptr() % 16 == 0
+
+
+@dataclass
+class Workspace:
+    """Caller-owned scratch + quantized operands of one problem shape (see Sage3Workspace in the C header)."""
+    buf: torch.Tensor            # uint8
+    layout: _cabi.Sage3Workspace
+
+    def region(self, name: str, nbytes: int | None = None) -> torch.Tensor:
+        off = getattr(self.layout, name)
+        return self.buf[off: off + nbytes] if nbytes is not None else self.buf[off:]
+
+
+class Sage3Problem:
+    """Shapes, strides and workspace of one call; reusable while shapes, strides and dtype stay the same."""
+
+    def __init__(self, q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, per_block_mean=True,
+                 out: torch.Tensor | None = None, workspace: torch.Tensor | None = None):
+        if tensor_layout not in ("HND", "NHD"):
+            raise ValueError(f"tensor_layout must be 'HND' or 'NHD', got {tensor_layout!r}")
+        for name, t in (("q", q), ("k", k), ("v", v)):
+            if t.dim() != 4:
+                raise ValueError(f"{name} must have 4 dimensions, got {t.dim()}")
+            if not t.is_cuda:
+                raise RuntimeError(f"{name} must be a CUDA tensor: sageattention_b200 has no CPU path")
+        if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
+            raise TypeError("q, k, v must share dtype torch.float16 or torch.bfloat16")
+        if not (q.device == k.device == v.device):
+            raise RuntimeError("q, k, v must be on the same device")
+        if torch.cuda.get_device_capability(q.device) != (10, 0):
+            raise RuntimeError("sageattention_b200 runs on compute capability 10.0 (B200) only")
+        hd, nd = (1, 2) if tensor_layout == "HND" else (2, 1)
+        B, Hq, Nq, D = q.shape[0], q.shape[hd], q.shape[nd], q.shape[3]
+        Hkv, Nk = k.shape[hd], k.shape[nd]
+        if k.shape[0] != B or v.shape != k.shape or k.shape[3] != D:
+            raise ValueError("k and v must have the shape of q except for the head and sequence dimensions")
+        if D not in (64, 128):
+            raise ValueError(f"head dim must be 64 or 128, got {D}")
+        if Hq % Hkv != 0:
+            raise ValueError(f"number of query heads ({Hq}) must be a multiple of kv heads ({Hkv})")
+        self.q = q if _usable(q) else q.contiguous()
+        self.k = k if _usable(k) else k.contiguous()
+        self.v = v if _usable(v) else v.contiguous()
+        if out is None:
+            out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        elif out.shape != q.shape or out.dtype != q.dtype or not _usable(out):
+            raise ValueError("out must match q in shape and dtype, with 16-byte aligned rows")
+        self.out = out
+        self.tensor_layout = tensor_layout
+        self.device = q.device
+
+        d = _cabi.Sage3Desc()
+        d.B, d.Hq, d.Hkv, d.Nq, d.Nk, d.D = B, Hq, Hkv, Nq, Nk, D
+        d.dtype = _DTYPES[q.dtype]
+        d.is_causal = int(bool(is_causal))
+        d.per_block_mean = int(bool(per_block_mean))
+        d.q_stride = (C.c_int64 * 3)(*_bhn_strides(self.q, tensor_layout))
+        d.k_stride = (C.c_int64 * 3)(*_bhn_strides(self.k, tensor_layout))
+        d.v_stride = (C.c_int64 * 3)(*_bhn_strides(self.v, tensor_layout))
+        d.o_stride = (C.c_int64 * 3)(*_bhn_strides(self.out, tensor_layout))
+        self._scale_tensor = None
+        if sm_scale is None:
+            d.sm_scale = 0.0
+        elif isinstance(sm_scale, torch.Tensor) and sm_scale.numel() > 1:
+            if sm_scale.numel() != Hq:
+                raise ValueError(f"a per-head sm_scale must have {Hq} elements")
+            self._scale_tensor = sm_scale.detach().to(device=q.device, dtype=torch.float32).contiguous()
+            d.sm_scale_per_head = self._scale_tensor.data_ptr()
+        else:
+            d.sm_scale = float(sm_scale)
+            if not d.sm_scale > 0:
+                raise ValueError("sm_scale must be positive")
+        self.desc = d
+
+        lay = _cabi.Sage3Workspace()
+        _cabi.check(_cabi.lib().sage3_workspace_layout(C.byref(d), C.byref(lay)), "sage3_workspace_layout")
+        if workspace is None:
+            workspace = torch.empty(lay.total_bytes + 256, dtype=torch.uint8, device=q.device)
+        elif workspace.numel() < lay.total_bytes + 256 or workspace.dtype != torch.uint8 or workspace.device != q.device:
+            raise ValueError(f"workspace must be a uint8 CUDA tensor of at least {lay.total_bytes + 256} bytes")
+        shift = (-workspace.data_ptr()) % 256
+        self.ws = Workspace(workspace[shift: shift + lay.total_bytes], lay)
+
+    # -- launches -------------------------------------------------------------------------------------
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def prepass(self) -> None:
+        with torch.cuda.device(self.device):
+            _cabi.check(_cabi.lib().sage3_prepass(C.byref(self.desc), self.q.data_ptr(), self.k.data_ptr(),
+                                                  self.v.data_ptr(), self.ws.buf.data_ptr(), self._stream()),
+                        "sage3_prepass")
+
+    def attention(self, debug: torch.Tensor | None = None) -> torch.Tensor:
+        with torch.cuda.device(self.device):
+            if debug is None:
+                rc = _cabi.lib().sage3_attn_fwd(C.byref(self.desc), self.ws.buf.data_ptr(), self.out.data_ptr(), None,
+                                                self._stream())
+            else:
+                rc = _cabi.lib().sage3_attn_fwd_debug(C.byref(self.desc), self.ws.buf.data_ptr(), self.out.data_ptr(),
+                                                      debug.data_ptr(), self._stream())
+            _cabi.check(rc, "sage3_attn_fwd")
+        return self.out
+
+    def run(self) -> torch.Tensor:
+        with torch.cuda.device(self.device):
+            _cabi.check(_cabi.lib().sage3_fwd(C.byref(self.desc), self.q.data_ptr(), self.k.data_ptr(),
+                                              self.v.data_ptr(), self.ws.buf.data_ptr(), self.out.data_ptr(), None,
+                                              self._stream()), "sage3_fwd")
+        return self.out
+
+    def check_status(self) -> int:
+        """Synchronizes and returns the device status word (0 = fine); raises if a bounded wait gave up."""
+        word = C.c_int32(0)
+        with torch.cuda.device(self.device):
+            rc = _cabi.lib().sage3_check_status(self.ws.buf.data_ptr(), C.byref(word), self._stream())
+        if rc == _cabi.SAGE3_E_DEVICE_WAIT:
+            raise _cabi.Sage3Error(rc, f"device status word {word.value}")
+        _cabi.check(rc, "sage3_check_status")
+        return word.value
+
+
+def sageattn3(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND", is_causal: bool = False,
+              sm_scale=None, per_block_mean: bool = True, return_lse: bool = False, attn_mask=None,
+              workspace: torch.Tensor | None = None, **kwargs) -> torch.Tensor:
+    """SageAttention3 (NVFP4 attention) on B200.
+
+    q: [B, Hq, Nq, D] ("HND") or [B, Nq, Hq, D] ("NHD"); k, v likewise with Hkv, Nk.  fp16 or bf16 CUDA
+    tensors, D in {64, 128}.  Returns a tensor shaped and typed like q.  `sm_scale` defaults to D**-0.5 and
+    may be a float or a tensor with one scale per query head.  Extra keyword arguments (dropout_p, scale, ...)
+    are accepted and ignored, as the reference does, so the function can replace
+    F.scaled_dot_product_attention in place.
+    """
+    if attn_mask is not None:
+        raise NotImplementedError("attn_mask is not supported by the FP4 attention path")
+    if return_lse:
+        raise NotImplementedError("return_lse is not available yet (the reference's FP4 kernel never writes its LSE either)")
+    if sm_scale is None and kwargs.get("scale") is not None:
+        sm_scale = kwargs["scale"]          # F.scaled_dot_product_attention's name for the same thing
+    prob = Sage3Problem(q, k, v, tensor_layout, is_causal, sm_scale, per_block_mean, workspace=workspace)
+    return prob.run()
+
+
+def sageattn3_blackwell(q, k, v, attn_mask=None, is_causal=False, per_block_mean=True, **kwargs):
+    """Signature of the reference's v3 entry (api.py:131): HND layout, D**-0.5 scale."""
+    return sageattn3(q, k, v, tensor_layout="HND", is_causal=is_causal, per_block_mean=per_block_mean,
+                     attn_mask=attn_mask, **kwargs)
+
+
+def sageattn(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, return_lse=False, **kwargs):
+    """Signature of the reference's v2 dispatcher (core.py:79-88); on B200 it always runs the FP4 path."""
+    return sageattn3(q, k, v, tensor_layout=tensor_layout, is_causal=is_causal, sm_scale=sm_scale,
+                     return_lse=return_lse, **kwargs)

@@ -1,0 +1,194 @@
+// extern "C" boundary of libsage3_b200.so (declared in include/sage3_b200.h): argument validation,
+// workspace layout, and the launches.  No allocation, no caching of caller pointers, no exceptions.
+#include <cuda_runtime.h>
+
+#include "../../include/sage3_b200.h"
+#include "sage3_common.cuh"
+#include "sage3_kernels.h"
+
+namespace {
+
+constexpr size_t kAlign = 1024;     // every workspace region starts at a multiple of this from the base
+constexpr size_t kWsAlign = 256;    // required alignment of the workspace base pointer
+inline size_t align_up(size_t x) { return (x + kAlign - 1) / kAlign * kAlign; }
+
+int validate(const Sage3Desc* d) {
+    if (!d) return SAGE3_E_NULL;
+    if (d->B <= 0 || d->Hq <= 0 || d->Hkv <= 0 || d->Nq <= 0 || d->Nk <= 0) return SAGE3_E_SHAPE;
+    if (d->D != 64 && d->D != 128) return SAGE3_E_SHAPE;
+    if (d->Hq % d->Hkv != 0) return SAGE3_E_SHAPE;
+    if (d->dtype != SAGE3_FP16 && d->dtype != SAGE3_BF16) return SAGE3_E_DTYPE;
+    // 128-bit loads and stores need every row to start on a 16-byte boundary: strides are multiples of 8 elements
+    const int64_t* strides[4] = {d->q_stride, d->k_stride, d->v_stride, d->o_stride};
+    for (auto s : strides)
+        for (int i = 0; i < 3; ++i)
+            if (s[i] < 0 || (s[i] % 8) != 0) return SAGE3_E_STRIDE;
+    // index arithmetic inside the kernels is 32-bit for tile counts
+    const int64_t nqp = ((int64_t)d->Nq + 127) / 128 * 128, nkp = ((int64_t)d->Nk + 127) / 128 * 128;
+    if (nqp > (1 << 24) || nkp > (1 << 24)) return SAGE3_E_TOO_LARGE;
+    if ((int64_t)d->B * d->Hq * (nqp / 128) > 0x7fffffffLL) return SAGE3_E_TOO_LARGE;
+    return SAGE3_OK;
+}
+
+int layout(const Sage3Desc* d, Sage3Workspace* w) {
+    const int rc = validate(d);
+    if (rc != SAGE3_OK) return rc;
+    if (!w) return SAGE3_E_NULL;
+    const size_t B = d->B, Hq = d->Hq, Hkv = d->Hkv, D = d->D;
+    const size_t nqp = ((size_t)d->Nq + 127) / 128 * 128, nkp = ((size_t)d->Nk + 127) / 128 * 128;
+    const size_t nqm = d->per_block_mean ? nqp / 128 : 1;
+    const size_t kch_k = ((size_t)d->Nk + sage3::kRowsPerChunk - 1) / sage3::kRowsPerChunk;
+    const size_t kch_q = ((size_t)d->Nq + sage3::kRowsPerChunk - 1) / sage3::kRowsPerChunk;
+    size_t part = B * Hkv * kch_k;
+    if (!d->per_block_mean && B * Hq * kch_q > part) part = B * Hq * kch_q;
+    size_t off = 0;
+    w->status = off;  off += align_up(64 * sizeof(int32_t));
+    w->kpart = off;   off += align_up(part * D * sizeof(float));
+    w->km = off;      off += align_up(B * Hkv * D * 2);
+    w->qm = off;      off += align_up(B * Hq * nqm * D * 2);
+    w->delta = off;   off += align_up(B * Hq * nqm * nkp * 2);
+    w->q_codes = off; off += align_up(B * Hq * nqp * (D / 2));
+    w->q_sf = off;    off += align_up(B * Hq * (nqp / 128) * (D / 64) * 512);
+    w->k_codes = off; off += align_up(B * Hkv * nkp * (D / 2));
+    w->k_sf = off;    off += align_up(B * Hkv * (nkp / 128) * (D / 64) * 512);
+    w->v_codes = off; off += align_up(B * Hkv * D * (nkp / 2));
+    w->v_sf = off;    off += align_up(B * Hkv * (nkp / 128) * 1024);
+    w->total_bytes = off;
+    w->nq_pad = (int32_t)nqp;
+    w->nk_pad = (int32_t)nkp;
+    w->nqm = (int32_t)nqm;
+    w->kchunks = (int32_t)kch_k;
+    return SAGE3_OK;
+}
+
+int check_arch() {
+    int dev = 0, major = 0, minor = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return SAGE3_E_CUDA;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return SAGE3_E_CUDA;
+    if (cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev) != cudaSuccess) return SAGE3_E_CUDA;
+    return (major == 10 && minor == 0) ? SAGE3_OK : SAGE3_E_ARCH;
+}
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+int attn_impl(const Sage3Desc* desc, void* ws, void* out, float* lse, float* debug, void* stream) {
+    Sage3Workspace w;
+    int rc = layout(desc, &w);
+    if (rc != SAGE3_OK) return rc;
+    if (!ws || !out) return SAGE3_E_NULL;
+    if (lse != nullptr) return SAGE3_E_SHAPE;   // reserved
+    if (!aligned(ws, kWsAlign) || !aligned(out, 16)) return SAGE3_E_ALIGN;
+    rc = check_arch();
+    if (rc != SAGE3_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    if (cudaMemsetAsync(base + w.status, 0, 64 * sizeof(int32_t), st) != cudaSuccess) return SAGE3_E_CUDA;
+    sage3::AttnArgs a;
+    a.B = desc->B; a.Hq = desc->Hq; a.Hkv = desc->Hkv; a.Nq = desc->Nq; a.Nk = desc->Nk; a.D = desc->D;
+    a.Nq_p = w.nq_pad; a.Nk_p = w.nk_pad; a.nqm = w.nqm;
+    a.is_causal = desc->is_causal != 0;
+    a.is_bf16 = desc->dtype == SAGE3_BF16;
+    a.sm_scale = desc->sm_scale > 0.f ? desc->sm_scale : 1.0f / sqrtf((float)desc->D);
+    a.sm_scale_per_head = desc->sm_scale_per_head;
+    a.delta = base + w.delta;
+    a.q_codes = base + w.q_codes; a.q_sf = base + w.q_sf;
+    a.k_codes = base + w.k_codes; a.k_sf = base + w.k_sf;
+    a.v_codes = base + w.v_codes; a.v_sf = base + w.v_sf;
+    a.out = out;
+    for (int i = 0; i < 3; ++i) a.os[i] = desc->o_stride[i];
+    a.status = reinterpret_cast<int*>(base + w.status);
+    a.debug = debug;
+    int drv = 0;
+    return sage3::launch_attn(a, st, &drv) == cudaSuccess ? SAGE3_OK : SAGE3_E_CUDA;
+}
+
+}  // namespace
+
+extern "C" {
+
+SAGE3_API int sage3_version(void) { return SAGE3_ABI_VERSION; }
+
+SAGE3_API const char* sage3_strerror(int code) {
+    switch (code) {
+        case SAGE3_OK: return "ok";
+        case SAGE3_E_NULL: return "a required pointer is NULL";
+        case SAGE3_E_SHAPE: return "unsupported shape (D must be 64 or 128, Hq a multiple of Hkv, sizes positive, lse NULL)";
+        case SAGE3_E_DTYPE: return "dtype must be SAGE3_FP16 or SAGE3_BF16";
+        case SAGE3_E_STRIDE: return "strides must be non-negative multiples of 8 elements with the last dimension contiguous";
+        case SAGE3_E_ALIGN: return "pointer alignment: tensors 16 bytes, workspace 256 bytes";
+        case SAGE3_E_ARCH: return "the current CUDA device is not compute capability 10.0 (B200)";
+        case SAGE3_E_CUDA: return "a CUDA call or kernel launch failed";
+        case SAGE3_E_TOO_LARGE: return "a size exceeds a fixed limit of this entry point";
+        case SAGE3_E_DEVICE_WAIT: return "a bounded device-side wait gave up (see the status word)";
+        default: return "unknown status code";
+    }
+}
+
+SAGE3_API int sage3_workspace_layout(const Sage3Desc* desc, Sage3Workspace* ws) { return layout(desc, ws); }
+
+SAGE3_API size_t sage3_workspace_bytes(const Sage3Desc* desc) {
+    Sage3Workspace w;
+    return layout(desc, &w) == SAGE3_OK ? w.total_bytes : 0;
+}
+
+SAGE3_API int sage3_prepass(const Sage3Desc* desc, const void* q, const void* k, const void* v, void* ws, void* stream) {
+    Sage3Workspace w;
+    int rc = layout(desc, &w);
+    if (rc != SAGE3_OK) return rc;
+    if (!q || !k || !v || !ws) return SAGE3_E_NULL;
+    if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(ws, kWsAlign)) return SAGE3_E_ALIGN;
+    rc = check_arch();
+    if (rc != SAGE3_OK) return rc;
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    sage3::PrepassArgs a;
+    a.q = q; a.k = k; a.v = v;
+    for (int i = 0; i < 3; ++i) {
+        a.qs[i] = desc->q_stride[i];
+        a.ks[i] = desc->k_stride[i];
+        a.vs[i] = desc->v_stride[i];
+    }
+    a.B = desc->B; a.Hq = desc->Hq; a.Hkv = desc->Hkv; a.Nq = desc->Nq; a.Nk = desc->Nk; a.D = desc->D;
+    a.Nq_p = w.nq_pad; a.Nk_p = w.nk_pad; a.nqm = w.nqm;
+    a.per_block_mean = desc->per_block_mean != 0;
+    a.is_bf16 = desc->dtype == SAGE3_BF16;
+    a.kchunks_k = w.kchunks;
+    a.kchunks_q = (desc->Nq + sage3::kRowsPerChunk - 1) / sage3::kRowsPerChunk;
+    a.kpart = reinterpret_cast<float*>(base + w.kpart);
+    a.km = base + w.km; a.qm = base + w.qm; a.delta = base + w.delta;
+    a.q_codes = base + w.q_codes; a.q_sf = base + w.q_sf;
+    a.k_codes = base + w.k_codes; a.k_sf = base + w.k_sf;
+    a.v_codes = base + w.v_codes; a.v_sf = base + w.v_sf;
+    return sage3::launch_prepass(a, static_cast<cudaStream_t>(stream)) == cudaSuccess ? SAGE3_OK : SAGE3_E_CUDA;
+}
+
+SAGE3_API int sage3_attn_fwd(const Sage3Desc* desc, void* ws, void* out, float* lse, void* stream) {
+    return attn_impl(desc, ws, out, lse, nullptr, stream);
+}
+
+SAGE3_API int sage3_attn_fwd_debug(const Sage3Desc* desc, void* ws, void* out, float* debug, void* stream) {
+    return attn_impl(desc, ws, out, nullptr, debug, stream);
+}
+
+SAGE3_API int sage3_fwd(const Sage3Desc* desc, const void* q, const void* k, const void* v, void* ws, void* out, float* lse,
+              void* stream) {
+    const int rc = sage3_prepass(desc, q, k, v, ws, stream);
+    if (rc != SAGE3_OK) return rc;
+    return sage3_attn_fwd(desc, ws, out, lse, stream);
+}
+
+SAGE3_API int sage3_check_status(const void* ws, int32_t* word, void* stream) {
+    if (!ws) return SAGE3_E_NULL;
+    int32_t host[64];
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cudaMemcpyAsync(host, ws, sizeof(host), cudaMemcpyDeviceToHost, st) != cudaSuccess) return SAGE3_E_CUDA;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return SAGE3_E_CUDA;
+    for (int i = 0; i < 64; ++i)
+        if (host[i] != 0) {
+            if (word) *word = host[i];
+            return SAGE3_E_DEVICE_WAIT;
+        }
+    if (word) *word = 0;
+    return SAGE3_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,39 @@
+// Host-visible launch interface between the C ABI (sage3_abi.cu) and the kernel translation units.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace sage3 {
+
+constexpr int kRowsPerChunk = 512;   // rows per partial column sum (fixes the summation order)
+
+struct PrepassArgs {
+    const void *q, *k, *v;
+    int64_t qs[3], ks[3], vs[3];   // element strides for (b, h, n)
+    int B, Hq, Hkv, Nq, Nk, D, Nq_p, Nk_p, nqm;
+    int per_block_mean, is_bf16;
+    int kchunks_k, kchunks_q;
+    float* kpart;
+    void *km, *qm, *delta;
+    uint8_t *q_codes, *q_sf, *k_codes, *k_sf, *v_codes, *v_sf;
+};
+
+struct AttnArgs {
+    int B, Hq, Hkv, Nq, Nk, D, Nq_p, Nk_p, nqm;
+    int is_causal, is_bf16;
+    float sm_scale;                 // already resolved (> 0)
+    const float* sm_scale_per_head; // device [Hq] or nullptr
+    const void* delta;              // dtype [B][Hq][nqm][Nk_p]
+    const uint8_t *q_codes, *q_sf, *k_codes, *k_sf, *v_codes, *v_sf;
+    void* out;
+    int64_t os[3];
+    int* status;
+    float* debug;                   // optional diagnostics dump of the first CTA; nullptr in normal use
+};
+
+cudaError_t launch_prepass(const PrepassArgs& a, cudaStream_t st);
+// returns cudaSuccess, or an error; `driver_rc` receives a CUresult when tensor-map encoding failed
+cudaError_t launch_attn(const AttnArgs& a, cudaStream_t st, int* driver_rc);
+
+}  // namespace sage3

@@ -1,0 +1,420 @@
+// Pre-pass kernels: K smoothing, Q smoothing, delta_s = qm . k'^T, and NVFP4 quantization of Q, K and
+// V-transposed into the layouts the attention kernel consumes.  HBM-bound; 128-bit loads, staged and
+// coalesced stores.
+//
+// Math follows (paths inside the reference project, sageattention3_blackwell/sageattn3/...):
+//   api.py:84            k' = k - mean_N(k)                 (mean: fp32 sum, rounded to the input type)
+//   api.py:55-72, 86-90  q' = q - mean of each 128-row block (or of all padded rows)
+//   api.py:91            delta_s = qm . k'^T, rounded to the input type
+//   quantization/fp4_quantization_4d.cu:185-225   SF = e4m3(amax / 6), code = e2m1(x * (1 / SF))
+//   quantization/fp4_quantization_4d.cu:300-349   V: microblocks are 16 consecutive tokens of one channel
+// Divisions and reciprocals are IEEE (div.rn / rcp.rn) so the result can be checked bit for bit.
+#include "sage3_common.cuh"
+#include "sage3_kernels.h"
+
+namespace sage3 {
+
+template <typename T> struct Num;
+template <> struct Num<__nv_bfloat16> {
+    using T2 = __nv_bfloat162;
+    static __device__ __forceinline__ float to_f(__nv_bfloat16 x) { return __bfloat162float(x); }
+    static __device__ __forceinline__ __nv_bfloat16 from_f(float x) { return __float2bfloat16_rn(x); }
+    static __device__ __forceinline__ float2 to_f2(uint32_t w) {
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+    }
+};
+template <> struct Num<__half> {
+    using T2 = __half2;
+    static __device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
+    static __device__ __forceinline__ __half from_f(float x) { return __float2half_rn(x); }
+    static __device__ __forceinline__ float2 to_f2(uint32_t w) {
+        return __half22float2(*reinterpret_cast<const __half2*>(&w));
+    }
+};
+
+template <typename T>
+__device__ __forceinline__ void load16(const T* p, bool valid, float* f) {   // 16 elements -> fp32
+    uint4 a = make_uint4(0, 0, 0, 0), b = a;
+    if (valid) {
+        a = __ldg(reinterpret_cast<const uint4*>(p));
+        b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+    }
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float2 v = Num<T>::to_f2(w[i]);
+        f[2 * i] = v.x;
+        f[2 * i + 1] = v.y;
+    }
+}
+
+// One NVFP4 microblock: 16 fp32 values (already on the input type's grid) -> 8 bytes of codes + scale byte.
+__device__ __forceinline__ void quant16(const float* x, uint32_t& lo, uint32_t& hi, uint32_t& sf_byte) {
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
+    sf_byte = cvt_e4m3x2(__fdiv_rn(amax, 6.0f), 0.f) & 0xffu;
+    const float sf = e4m3_to_float(sf_byte);
+    const float inv = (sf == 0.f) ? 0.f : __frcp_rn(sf);
+    float y[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) y[i] = __fmul_rn(x[i], inv);
+    lo = cvt_e2m1x8(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7]);
+    hi = cvt_e2m1x8(y[8], y[9], y[10], y[11], y[12], y[13], y[14], y[15]);
+}
+
+// ------------------------------------------------------------------------------------------------
+// column sums over tokens: partial sums per chunk of kRowsPerChunk rows, then a fixed-order finalize
+// (deterministic: no atomics, the summation order depends on N only)
+// ------------------------------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void __launch_bounds__(256) colsum_partial_kernel(const T* __restrict__ x, int64_t sb, int64_t sh,
+                                                             int64_t sn, int H, int N,
+                                                             float* __restrict__ part, int chunks) {
+    constexpr int TPR = D / 8;           // threads per row (8 elements = 16 bytes each)
+    constexpr int RPP = 256 / TPR;       // rows per pass
+    const int chunk = blockIdx.x, bh = blockIdx.y;
+    const int b = bh / H, h = bh % H;
+    const T* base = x + b * sb + h * sh;
+    const int c8 = threadIdx.x % TPR, rl = threadIdx.x / TPR;
+    const int r0 = chunk * kRowsPerChunk;
+    const int r1 = min(N, r0 + kRowsPerChunk);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int r = r0 + rl; r < r1; r += RPP) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)r * sn + c8 * 8));
+        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 v = Num<T>::to_f2(w[i]);
+            acc[2 * i] += v.x;
+            acc[2 * i + 1] += v.y;
+        }
+    }
+    __shared__ float red[RPP][D + 1];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[rl][c8 * 8 + i] = acc[i];
+    __syncthreads();
+    if (threadIdx.x < D) {
+        float s = 0.f;
+#pragma unroll 4
+        for (int i = 0; i < RPP; ++i) s += red[i][threadIdx.x];
+        part[((int64_t)bh * chunks + chunk) * D + threadIdx.x] = s;
+    }
+}
+
+template <typename T, int D>
+__global__ void colmean_finalize_kernel(const float* __restrict__ part, int chunks, float inv_count,
+                                        T* __restrict__ mean) {
+    const int bh = blockIdx.x, d = threadIdx.x;
+    float s = 0.f;
+    for (int c = 0; c < chunks; ++c) s += part[((int64_t)bh * chunks + c) * D + d];
+    mean[(int64_t)bh * D + d] = Num<T>::from_f(s * inv_count);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Q / K: smooth + quantize one 128-row tile per CTA; K tiles also produce their delta_s columns
+// ------------------------------------------------------------------------------------------------
+enum { kModeQBlockMean = 0, kModeQGlobalMean = 1, kModeK = 2 };
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+template <typename T>
+__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__half>(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename T, int D, int MODE>
+__global__ void __launch_bounds__(256) quant_rows_kernel(
+    const T* __restrict__ x, int64_t sb, int64_t sh, int64_t sn, int H, int N, int Np,
+    const T* __restrict__ mean_in,     // K: km [B*H][D]; Q global mean: qm [B*H][D]; unused for block mean
+    T* __restrict__ qm_out,            // Q block mean: [B*H][Np/128][D]
+    uint8_t* __restrict__ codes,       // [B*H][Np][D/2]
+    uint8_t* __restrict__ sfs,         // [B*H][Np/128][D/64][512]
+    // K mode only: delta_s
+    const T* __restrict__ qm_all,      // [B][Hq][nqm][D]
+    T* __restrict__ delta,             // [B][Hq][nqm][Np]
+    int Hq, int nqm) {
+    constexpr int CH = D / 16;            // microblocks per row
+    constexpr int RPP = 256 / CH;         // rows per pass
+    constexpr int ITEMS = kBlock / RPP;   // microblocks per thread
+    constexpr int PITCH = D + 8;          // smem row pitch in elements (odd multiple of 16 bytes)
+    constexpr int MCH = 64;               // query blocks per delta_s pass
+
+    const int tile = blockIdx.x, bh = blockIdx.y;
+    const int b = bh / H, h = bh % H;
+    const int t = threadIdx.x;
+    const int c = t % CH, rl = t / CH;
+    const T* base = x + b * sb + h * sh;
+    const int row0 = tile * kBlock;
+
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    float* s_mean = reinterpret_cast<float*>(smem_raw);                        // [D]
+    uint8_t* s_sf = smem_raw + D * 4;                                          // [(D/64) * 512]
+    float* s_red = reinterpret_cast<float*>(s_sf + (D / 64) * 512);            // [8 warps][D] (block mean)
+    T* s_k = reinterpret_cast<T*>(reinterpret_cast<uint8_t*>(s_red) + 8 * D * 4);   // [128][PITCH]  (K mode)
+    T* s_a = s_k + kBlock * PITCH;                                                  // [MCH][PITCH] (K mode)
+
+    float v[ITEMS][16];
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        const int r = row0 + rl + RPP * i;
+        load16<T>(base + (int64_t)r * sn + c * 16, r < N, v[i]);
+    }
+
+    if (MODE == kModeQBlockMean) {
+        // column sums over the tile's 128 rows (rows beyond N are zero and count, as padding precedes the mean)
+        float acc[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < ITEMS; ++i) s += v[i][j];
+            acc[j] = s;
+        }
+        // lanes sharing c inside a warp: lane = c + CH * k
+#pragma unroll
+        for (int off = CH; off < 32; off <<= 1) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
+        }
+        const int warp = t >> 5, lane = t & 31;
+        if (lane < CH) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) s_red[warp * D + lane * 16 + j] = acc[j];
+        }
+        __syncthreads();
+        if (t < D) {
+            float s = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) s += s_red[w * D + t];
+            const T m = Num<T>::from_f(s * (1.0f / kBlock));
+            s_mean[t] = Num<T>::to_f(m);
+            qm_out[((int64_t)bh * (Np / kBlock) + tile) * D + t] = m;
+        }
+    } else {
+        if (t < D) s_mean[t] = Num<T>::to_f(mean_in[(int64_t)bh * D + t]);
+    }
+    __syncthreads();
+
+    float mu[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) mu[j] = s_mean[c * 16 + j];
+
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        const int rt = rl + RPP * i;          // row inside the tile
+        const int r = row0 + rt;
+        float y[16];
+        const bool zero_row = (MODE == kModeK) && (r >= N);   // K is padded after smoothing: pad rows are 0
+#pragma unroll
+        for (int j = 0; j < 16; ++j) y[j] = zero_row ? 0.f : Num<T>::to_f(Num<T>::from_f(v[i][j] - mu[j]));
+        uint32_t lo, hi, sfb;
+        quant16(y, lo, hi, sfb);
+        *reinterpret_cast<uint2*>(codes + ((int64_t)bh * Np + r) * (D / 2) + c * 8) = make_uint2(lo, hi);
+        s_sf[sf_atom_offset(rt, c)] = static_cast<uint8_t>(sfb);
+        if (MODE == kModeK) {
+            // keep k' for the delta_s product
+            typename Num<T>::T2* dst = reinterpret_cast<typename Num<T>::T2*>(s_k + rt * PITCH + c * 16);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                typename Num<T>::T2 p;
+                p.x = Num<T>::from_f(y[2 * j]);
+                p.y = Num<T>::from_f(y[2 * j + 1]);
+                dst[j] = p;
+            }
+        }
+    }
+    __syncthreads();
+    // scale factors of the tile: (D/64) atoms of 512 bytes, contiguous
+    {
+        uint8_t* dst = sfs + ((int64_t)bh * (Np / kBlock) + tile) * (D / 64) * 512;
+        if (t < (D / 64) * 32) reinterpret_cast<uint4*>(dst)[t] = reinterpret_cast<const uint4*>(s_sf)[t];
+    }
+
+    if (MODE == kModeK) {
+        // delta_s[b][hq][qb][row0 + n] = sum_d qm[b][hq][qb][d] * k'[n][d] for every query head of this kv head
+        const int group = Hq / H;
+        const int warp = t >> 5, lane = t & 31;
+        const uint32_t sk_addr = smem_u32(s_k), sa_addr = smem_u32(s_a);
+        for (int g = 0; g < group; ++g) {
+            const int hq = h * group + g;
+            const T* qmh = qm_all + ((int64_t)b * Hq + hq) * nqm * D;
+            T* dh = delta + ((int64_t)b * Hq + hq) * nqm * (int64_t)Np;
+            for (int m0 = 0; m0 < nqm; m0 += MCH) {
+                __syncthreads();   // previous pass done with s_a
+                for (int idx = t; idx < MCH * (D / 8); idx += 256) {
+                    const int r = idx / (D / 8), c8 = idx % (D / 8);
+                    uint4 val = make_uint4(0, 0, 0, 0);
+                    if (m0 + r < nqm) val = __ldg(reinterpret_cast<const uint4*>(qmh + (int64_t)(m0 + r) * D + c8 * 8));
+                    *reinterpret_cast<uint4*>(s_a + r * PITCH + c8 * 8) = val;
+                }
+                __syncthreads();
+                float acc[MCH / 16][2][4];
+#pragma unroll
+                for (int mt = 0; mt < MCH / 16; ++mt)
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) acc[mt][nt][e] = 0.f;
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    uint32_t bf[4];
+                    {   // B: keys [16 * warp, +16), k [16 * ks, +16): matrices (n-tile, k-half)
+                        const int i = lane >> 3;
+                        const int n = warp * 16 + (lane & 7) + 8 * (i >> 1);
+                        const int kk = ks * 16 + 8 * (i & 1);
+                        ldmatrix_x4(sk_addr + (n * PITCH + kk) * 2, bf[0], bf[1], bf[2], bf[3]);
+                    }
+#pragma unroll
+                    for (int mt = 0; mt < MCH / 16; ++mt) {
+                        uint32_t af[4];
+                        const int i = lane >> 3;
+                        const int r = mt * 16 + (lane & 7) + 8 * (i & 1);
+                        const int kk = ks * 16 + 8 * (i >> 1);
+                        ldmatrix_x4(sa_addr + (r * PITCH + kk) * 2, af[0], af[1], af[2], af[3]);
+                        mma16816<T>(acc[mt][0], af, bf[0], bf[1]);
+                        mma16816<T>(acc[mt][1], af, bf[2], bf[3]);
+                    }
+                }
+#pragma unroll
+                for (int mt = 0; mt < MCH / 16; ++mt)
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {
+                            const int qb = m0 + mt * 16 + (lane >> 2) + 8 * half;
+                            if (qb < nqm) {
+                                const int n = row0 + warp * 16 + nt * 8 + 2 * (lane & 3);
+                                typename Num<T>::T2 p;
+                                p.x = Num<T>::from_f(acc[mt][nt][2 * half]);
+                                p.y = Num<T>::from_f(acc[mt][nt][2 * half + 1]);
+                                *reinterpret_cast<typename Num<T>::T2*>(dh + (int64_t)qb * Np + n) = p;
+                            }
+                        }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// V: one tile of 128 tokens x D channels per CTA -> V^T codes (microblocks along tokens) + scale atoms
+// ------------------------------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void __launch_bounds__(256) quant_vt_kernel(const T* __restrict__ x, int64_t sb, int64_t sh, int64_t sn,
+                                                       int H, int N, int Np, uint8_t* __restrict__ codes,
+                                                       uint8_t* __restrict__ sfs) {
+    constexpr int PITCH = D + 2;          // elements; word pitch odd -> column reads are conflict-free
+    const int tile = blockIdx.x, bh = blockIdx.y;
+    const int b = bh / H, h = bh % H;
+    const int t = threadIdx.x;
+    const T* base = x + b * sb + h * sh;
+    const int row0 = tile * kBlock;
+
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    T* s_v = reinterpret_cast<T*>(smem_raw);                                  // [128][PITCH]
+    constexpr int OPITCH = 72;            // bytes per staged output row (64 + 8: 8-byte stores stay conflict-free)
+    uint8_t* s_out = smem_raw + ((kBlock * PITCH * 2 + 15) / 16) * 16;          // [D][OPITCH] codes
+    uint8_t* s_sf = s_out + D * OPITCH;                                        // [2 * 512]
+
+    // zero the scale atoms (rows >= D of a 128-row atom stay zero)
+    if (t < 64) reinterpret_cast<uint4*>(s_sf)[t] = make_uint4(0, 0, 0, 0);
+    // coalesced load: 16 bytes per thread per pass
+    constexpr int TPR = D / 8, RPP = 256 / TPR;
+    for (int r = t / TPR; r < kBlock; r += RPP) {
+        const int c8 = t % TPR;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (row0 + r < N) val = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)(row0 + r) * sn + c8 * 8));
+        uint32_t* dst = reinterpret_cast<uint32_t*>(s_v + r * PITCH + c8 * 8);   // 4-byte aligned (PITCH even)
+        dst[0] = val.x; dst[1] = val.y; dst[2] = val.z; dst[3] = val.w;
+    }
+    __syncthreads();
+    // microblock (channel d, token group mb): channel fastest across threads
+    for (int item = t; item < D * 8; item += 256) {
+        const int d = item % D, mb = item / D;
+        float y[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) y[i] = Num<T>::to_f(s_v[(mb * 16 + i) * PITCH + d]);
+        uint32_t lo, hi, sfb;
+        quant16(y, lo, hi, sfb);
+        *reinterpret_cast<uint2*>(s_out + d * OPITCH + mb * 8) = make_uint2(lo, hi);
+        s_sf[sf_atom_offset(d, mb)] = static_cast<uint8_t>(sfb);
+    }
+    __syncthreads();
+    // coalesced stores: D rows of 64 bytes
+    for (int idx = t; idx < D * 8; idx += 256) {
+        const int d = idx >> 3, q = idx & 7;
+        *reinterpret_cast<uint2*>(codes + ((int64_t)bh * D + d) * (Np / 2) + tile * 64 + q * 8) =
+            *reinterpret_cast<const uint2*>(s_out + d * OPITCH + q * 8);
+    }
+    if (t < 64) {
+        uint8_t* dst = sfs + ((int64_t)bh * (Np / kBlock) + tile) * 1024;
+        reinterpret_cast<uint4*>(dst)[t] = reinterpret_cast<const uint4*>(s_sf)[t];
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host-side launch
+// ------------------------------------------------------------------------------------------------
+template <typename T, int D>
+static cudaError_t launch_prepass_t(const PrepassArgs& a, cudaStream_t st) {
+    const T* q = static_cast<const T*>(a.q);
+    const T* k = static_cast<const T*>(a.k);
+    const T* v = static_cast<const T*>(a.v);
+    T* km = static_cast<T*>(a.km);
+    T* qm = static_cast<T*>(a.qm);
+    T* delta = static_cast<T*>(a.delta);
+    const int BHq = a.B * a.Hq, BHkv = a.B * a.Hkv;
+
+    // K mean over its Nk tokens
+    colsum_partial_kernel<T, D><<<dim3(a.kchunks_k, BHkv), 256, 0, st>>>(k, a.ks[0], a.ks[1], a.ks[2], a.Hkv, a.Nk,
+                                                                         a.kpart, a.kchunks_k);
+    colmean_finalize_kernel<T, D><<<BHkv, D, 0, st>>>(a.kpart, a.kchunks_k, 1.0f / (float)a.Nk, km);
+
+    const size_t smem_q = D * 4 + (D / 64) * 512 + 8 * D * 4;
+    const size_t smem_k = smem_q + (size_t)(kBlock + 64) * (D + 8) * sizeof(T);
+    if (a.per_block_mean) {
+        quant_rows_kernel<T, D, kModeQBlockMean><<<dim3(a.Nq_p / kBlock, BHq), 256, smem_q, st>>>(
+            q, a.qs[0], a.qs[1], a.qs[2], a.Hq, a.Nq, a.Nq_p, nullptr, qm, a.q_codes, a.q_sf, nullptr, nullptr, 0, 0);
+    } else {
+        // one mean per head over the padded rows (api.py:88-90); kpart is free again: the K finalize has
+        // consumed it and stream order serializes the two uses
+        colsum_partial_kernel<T, D><<<dim3(a.kchunks_q, BHq), 256, 0, st>>>(q, a.qs[0], a.qs[1], a.qs[2], a.Hq, a.Nq,
+                                                                            a.kpart, a.kchunks_q);
+        colmean_finalize_kernel<T, D><<<BHq, D, 0, st>>>(a.kpart, a.kchunks_q, 1.0f / (float)a.Nq_p, qm);
+        quant_rows_kernel<T, D, kModeQGlobalMean><<<dim3(a.Nq_p / kBlock, BHq), 256, smem_q, st>>>(
+            q, a.qs[0], a.qs[1], a.qs[2], a.Hq, a.Nq, a.Nq_p, qm, nullptr, a.q_codes, a.q_sf, nullptr, nullptr, 0, 0);
+    }
+    cudaError_t e = cudaFuncSetAttribute(quant_rows_kernel<T, D, kModeK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem_k);
+    if (e != cudaSuccess) return e;
+    quant_rows_kernel<T, D, kModeK><<<dim3(a.Nk_p / kBlock, BHkv), 256, smem_k, st>>>(
+        k, a.ks[0], a.ks[1], a.ks[2], a.Hkv, a.Nk, a.Nk_p, km, nullptr, a.k_codes, a.k_sf, qm, delta, a.Hq, a.nqm);
+
+    const size_t smem_v = ((kBlock * (D + 2) * sizeof(T) + 15) / 16) * 16 + D * 72 + 1024;
+    e = cudaFuncSetAttribute(quant_vt_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_v);
+    if (e != cudaSuccess) return e;
+    quant_vt_kernel<T, D><<<dim3(a.Nk_p / kBlock, BHkv), 256, smem_v, st>>>(v, a.vs[0], a.vs[1], a.vs[2], a.Hkv, a.Nk,
+                                                                           a.Nk_p, a.v_codes, a.v_sf);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_prepass(const PrepassArgs& a, cudaStream_t st) {
+    if (a.is_bf16) {
+        return a.D == 128 ? launch_prepass_t<__nv_bfloat16, 128>(a, st) : launch_prepass_t<__nv_bfloat16, 64>(a, st);
+    }
+    return a.D == 128 ? launch_prepass_t<__half, 128>(a, st) : launch_prepass_t<__half, 64>(a, st);
+}
+
+}  // namespace sage3
