@@ -46,7 +46,7 @@ def test_prepass_matches_oracle(cuda_device, B, Hq, Hkv, Nq, Nk, D, dt, pbm, lay
     assert torch.equal(ws["q_sf"], ref.q_sf), "Q scale bytes"
     assert torch.equal(ws["k_sf"], ref.k_sf), "K scale bytes"
     assert torch.equal(ws["vt_sf"], ref.vt_sf), "V scale bytes"
-    assert ws["vt_sf_pad"].abs().max() == 0
+    assert ws["vt_sf_pad"].numel() == 0 or ws["vt_sf_pad"].abs().max() == 0   # rows >= D of a 128-row atom
     assert torch.equal(canon(ws["q_codes"]), canon(ref.q_codes)), "Q codes"
     assert torch.equal(canon(ws["k_codes"]), canon(ref.k_codes)), "K codes"
     assert torch.equal(canon(ws["vt_codes"]), canon(ref.vt_codes)), "V codes"
