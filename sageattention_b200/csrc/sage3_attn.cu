@@ -2,7 +2,7 @@
 // accumulators in tensor memory, exp2 online softmax, P re-quantized to NVFP4 before the PV MMA.
 //
 // One CTA per 128-row query tile.  Ten warps:
-//   warp 0      TMA producer (one lane): Q once, then K / V^T / scale atoms / delta_s row per KV block
+//   warp 0      TMA producer (one lane): Q once, then K (+ delta_s row) / V^T / scale atoms per KV block
 //   warp 1      MMA issuer (one lane) and owner of the tensor-memory allocation
 //   warps 2-9   softmax: thread (row r, column half) owns 64 of the 128 scores of its row per block;
 //               the two halves of a row exchange their block maximum through shared memory
@@ -11,7 +11,8 @@
 //
 // Arithmetic follows (paths inside the reference project, sageattention3_blackwell/sageattn3/blackwell/...):
 //   mainloop_tma_ws.h:509, 532-551, 865     KV blocks are walked from the last to the first
-//   mainloop_tma_ws.h:691-704, 718          S starts from the delta_s row of the query tile
+//   mainloop_tma_ws.h:691-704, 718          S starts from the delta_s row of the query tile (here: a rank-1
+//                                           16-bit MMA, ones (x) delta_s, issued before the FP4 MMAs)
 //   mainloop_tma_ws.h:732-748               masks (applied here on the real key index)
 //   softmax_fused.h:39-137                  running max per 128 keys, P~ = 2^(S s - m s) * 2688, row sum of the
 //                                           unquantized P~, microblock scale max(P~)/6 (E4M3 in the MMA)
@@ -19,6 +20,8 @@
 // Every wait is bounded (see mbar_wait); a wait that gives up records a code in the status word and the
 // CTA winds down without touching tensor memory it does not own.
 #include <cuda.h>
+
+#include <type_traits>
 
 #include "sage3_common.cuh"
 #include "sage3_kernels.h"
@@ -61,7 +64,9 @@ struct Cfg {
     static constexpr int oSfV = oSfK + kStages * 1024;
     static constexpr int oSfP = oSfV + kStages * 1024;
     static constexpr int oDelta = oSfP + 2 * 1024;
-    static constexpr int oMx = oDelta + kStages * 256;        // float [2][2][128]
+    static constexpr int kDeltaPitch = 512;                   // 256 B of delta_s + 256 B that stay zero
+    static constexpr int oOnes = oDelta + kStages * kDeltaPitch;   // 128 x 16 tile: column 0 = 1.0, rest 0
+    static constexpr int oMx = oOnes + 4096;                  // float [2][2][128]
     static constexpr int oBar = oMx + 2 * 2 * 128 * 4;
     static constexpr int kNumBars = 1 + 4 * kStages + 2 + 2 + 2 + 1 + 4;
     static constexpr int oMisc = oBar + kNumBars * 8;
@@ -145,6 +150,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int i = 0; i < 4; ++i) mbar_init(bar(bPair + i), 2);
         mbar_fence_init();
     }
+    {
+        // delta_s stages: the 256 bytes behind each row stay zero for the whole kernel; ones tile:
+        // [k chunk][row group][8 rows][16 bytes], 1.0 in element 0 of every row of chunk 0
+        uint4* z = reinterpret_cast<uint4*>(sgen + C::oDelta);
+        for (int i = threadIdx.x; i < (S * C::kDeltaPitch + 4096) / 16; i += blockDim.x) z[i] = make_uint4(0, 0, 0, 0);
+        __syncthreads();
+        if (threadIdx.x < 128) {
+            const uint16_t one = std::is_same<OutT, __nv_bfloat16>::value ? 0x3F80 : 0x3C00;
+            *reinterpret_cast<uint16_t*>(sgen + C::oOnes + threadIdx.x * 16) = one;
+        }
+        fence_proxy_async_smem();
+    }
     if (warp == 1) {
         tmem_alloc(smem_u32(tmem_slot), 512);
         tmem_relinquish();
@@ -172,16 +189,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             for (int j = 0; j < nb; ++j) {
                 const int n = nb - 1 - j, st = j % S;
                 if (j >= S && !mbar_wait(bar(bKE + st), ((j / S) - 1) & 1, abort_flag, p.status, kWaitKEmpty)) break;
-                mbar_expect_tx(bar(bKF + st), C::kKBytes + C::kSfQkBytes);
+                mbar_expect_tx(bar(bKF + st), C::kKBytes + C::kSfQkBytes + C::kDeltaBytes);
                 tma_load_3d(sbase + C::oK + st * 8192, &tm_k, bar(bKF + st), 0, n * kBlock, bhkv);
                 bulk_load(sbase + C::oSfK + st * 1024, p.k_sf + ((size_t)bhkv * p.nkb + n) * C::kSfQkBytes,
                           C::kSfQkBytes, bar(bKF + st));
+                bulk_load(sbase + C::oDelta + st * C::kDeltaPitch, dptr + (size_t)n * kBlock, C::kDeltaBytes, bar(bKF + st));
                 if (j >= S && !mbar_wait(bar(bVE + st), ((j / S) - 1) & 1, abort_flag, p.status, kWaitVEmpty)) break;
-                mbar_expect_tx(bar(bVF + st), C::kVBytes + C::kSfVBytes + C::kDeltaBytes);
+                mbar_expect_tx(bar(bVF + st), C::kVBytes + C::kSfVBytes);
                 tma_load_3d(sbase + C::oV + st * 8192, &tm_v, bar(bVF + st), n * 64, 0, bhkv);
                 bulk_load(sbase + C::oSfV + st * 1024, p.v_sf + ((size_t)bhkv * p.nkb + n) * C::kSfVBytes,
                           C::kSfVBytes, bar(bVF + st));
-                bulk_load(sbase + C::oDelta + st * 256, dptr + (size_t)n * kBlock, C::kDeltaBytes, bar(bVF + st));
             }
         }
         __syncwarp();
@@ -191,6 +208,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             constexpr uint32_t idesc_qk = make_idesc_nvfp4(128);
             constexpr uint32_t idesc_pv = make_idesc_nvfp4(D);
             const uint64_t q_desc = make_sdesc(sbase + C::oQ, 16, C::kSboQK, C::kSwzQK);
+            constexpr uint32_t idesc_delta = make_idesc_f16_bmn(128, sizeof(OutT) == 2 && std::is_same<OutT, __nv_bfloat16>::value);
+            const uint64_t ones_desc = make_sdesc(sbase + C::oOnes, 2048, 128, kSwzNone);
             auto issue_qk = [&](int j) -> bool {
                 const int st = j % S, bb = j & 1;
                 if (j >= 2 && !mbar_wait(bar(bSE + bb), ((j >> 1) - 1) & 1, abort_flag, p.status, kWaitSEmpty)) return false;
@@ -200,10 +219,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
                 for (int ks = 0; ks < D / 64; ++ks)
                     tc_cp_sf(tmem + C::cSfK + 4 * ks, make_sdesc(sbase + C::oSfK + st * 1024 + ks * 512, 0, 128, kSwzNone));
+                // S <- 1 (x) delta_s: A = [128 x 16] with ones in column 0 (K-major), B = the delta_s row read as an
+                // MN-major [16 x 128] operand whose rows 1..15 alias finite data and meet zeros in A
+                tc_mma_f16(tmem + (bb ? C::cS1 : C::cS0), ones_desc,
+                           make_sdesc(sbase + C::oDelta + st * C::kDeltaPitch, 16, 16, kSwzNone), idesc_delta, false);
 #pragma unroll
                 for (int ks = 0; ks < D / 64; ++ks)
                     tc_mma_nvfp4(tmem + (bb ? C::cS1 : C::cS0), q_desc + 2 * ks, k_desc + 2 * ks, idesc_qk,
-                                 tmem + C::cSfQ + 4 * ks, tmem + C::cSfK + 4 * ks, ks > 0);
+                                 tmem + C::cSfQ + 4 * ks, tmem + C::cSfK + 4 * ks, true);
                 tc_commit(bar(bKE + st));
                 tc_commit(bar(bSF + bb));
                 return true;
@@ -249,7 +272,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         bool alive = true;
 
         for (int j = 0; j < nb; ++j) {
-            const int n = nb - 1 - j, st = j % S, bb = j & 1;
+            const int n = nb - 1 - j, bb = j & 1;
             if (!warp_wait(bar(bSF + bb), (j >> 1) & 1, abort_flag, p.status, kWaitSFull)) { alive = false; break; }
             tc_fence_after();
             float s[64];
@@ -261,21 +284,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(bSE + bb));
 
-            // delta_s row of this query tile (travels with the V stage)
-            if (!warp_wait(bar(bVF + st), (j / S) & 1, abort_flag, p.status, kWaitDelta)) { alive = false; break; }
-            {
-                const uint4* dp = reinterpret_cast<const uint4*>(sgen + C::oDelta + st * 256 + half * 128);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint4 w = dp[i];
-                    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        s[8 * i + 2 * e] += delta_to_f<OutT>(ww[e] & 0xffffu);
-                        s[8 * i + 2 * e + 1] += delta_to_f<OutT>(ww[e] >> 16);
-                    }
-                }
-            }
             // masks on the real key index: keys beyond Nk, and (causal) keys after the diagonal
             const int key0 = n * kBlock + half * 64;
             const bool need_mask = ((n + 1) * kBlock > p.Nk) || (CAUSAL && (n * kBlock + kBlock - 1 > mt * kBlock + shift));
@@ -311,19 +319,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             uint32_t codes[8];
             uint32_t sfbytes = 0;
             float rowsum = 0.f;
+            const uint64_t sl2x2 = pack2f(sl2, sl2);
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
                 const bool gdead = (bm[g] == -INFINITY);
                 // E = P~ / sf = 6 * 2^((S - bm) s);   sf = max(P~) / 6 = 2^(bm s - max_scaled - log2 6)
                 const float c = gdead ? 0.f : fmaf(bm[g], sl2, -kLog2Of6);
                 const float sf = gdead ? 0.f : ex2_approx(fmaf(bm[g], sl2, -max_scaled) - kLog2Of6);
+                const uint64_t negc = pack2f(-c, -c);
                 float e[16];
+                uint64_t acc0 = 0, acc1 = 0;      // two packed partial sums (bit pattern of +0.0f pairs)
 #pragma unroll
-                for (int i = 0; i < 16; ++i) e[i] = ex2_approx(fmaf(s[16 * g + i], sl2, -c));
-                float se = 0.f;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) se += e[i];
-                rowsum = fmaf(sf, se, rowsum);
+                for (int i = 0; i < 8; ++i) {
+                    float a, b2;
+                    unpack2f(fma2(pack2f(s[16 * g + 2 * i], s[16 * g + 2 * i + 1]), sl2x2, negc), a, b2);
+                    e[2 * i] = ex2_approx(a);
+                    e[2 * i + 1] = ex2_approx(b2);
+                    if (i & 1) acc1 = add2(acc1, pack2f(e[2 * i], e[2 * i + 1]));
+                    else acc0 = add2(acc0, pack2f(e[2 * i], e[2 * i + 1]));
+                }
+                float se0, se1;
+                unpack2f(add2(acc0, acc1), se0, se1);
+                rowsum = fmaf(sf, se0 + se1, rowsum);
                 codes[2 * g] = cvt_e2m1x8(e[0], e[1], e[2], e[3], e[4], e[5], e[6], e[7]);
                 codes[2 * g + 1] = cvt_e2m1x8(e[8], e[9], e[10], e[11], e[12], e[13], e[14], e[15]);
                 sfbytes |= (cvt_e4m3x2(sf, 0.f) & 0xffu) << (8 * g);
@@ -355,8 +372,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                         const uint32_t o_addr = tmem + lane_addr + C::cO + half * (D / 2) + cc * 32;
                         tmem_ld32(o_addr, o);
                         tc_wait_ld();
+                        const uint64_t a2 = pack2f(alpha, alpha);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] *= alpha;
+                        for (int i = 0; i < 16; ++i) unpack2f(mul2(pack2f(o[2 * i], o[2 * i + 1]), a2), o[2 * i], o[2 * i + 1]);
                         tmem_st32(o_addr, o);
                     }
                     tc_wait_st();

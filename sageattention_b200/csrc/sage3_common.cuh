@@ -48,6 +48,31 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     return r;
 }
 
+// packed fp32 pairs (one issue slot for two lanes of math)
+__device__ __forceinline__ uint64_t pack2f(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2f(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 // ------------------------------------------------------------------------------------------------
 // number formats
 // ------------------------------------------------------------------------------------------------
@@ -200,6 +225,25 @@ __device__ __forceinline__ void tc_mma_nvfp4(uint32_t d_tmem, uint64_t a_desc, u
         "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate ? 1u : 0u), "r"(sfa_tmem), "r"(sfb_tmem)
         : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem], 16-bit operands (fp16 or bf16), fp32 accumulate, K = 16.
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate ? 1u : 0u)
+        : "memory");
+}
+
+// instruction descriptor of the 16-bit MMA: M = 128, N = n, fp32 accumulator, A K-major, B MN-major.
+//   bits 4-5: D format (1 = F32), 7-9 / 10-12: A / B format (0 = F16, 1 = BF16), bit 15 / 16: A / B major
+//   (0 = K, 1 = MN), bits 17-22: N >> 3, bits 24-28: M >> 4.
+__host__ __device__ constexpr uint32_t make_idesc_f16_bmn(int n, bool bf16) {
+    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | (1u << 16) |
+           (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
 }
 
 // instruction descriptor of the block-scaled NVFP4 MMA: M = 128, N = n, both operands K-major.
