@@ -1,13 +1,17 @@
 // Block-scaled FP4 attention for sm_100a: TMA-staged E2M1 tiles, tcgen05 NVFP4 MMAs with the S and O
 // accumulators in tensor memory, exp2 online softmax, P re-quantized to NVFP4 before the PV MMA.
 //
-// One CTA per 128-row query tile.  Ten warps:
-//   warp 0      TMA producer (one lane): Q once, then K (+ delta_s row) / V^T / scale atoms per KV block
-//   warp 1      MMA issuer (one lane) and owner of the tensor-memory allocation
-//   warps 2-9   softmax: thread (row r, column half) owns 64 of the 128 scores of its row per block;
-//               the two halves of a row exchange their block maximum through shared memory
-// S is double-buffered in tensor memory so that Q K^T of block j+1 overlaps the softmax of block j.
-// O stays in tensor memory and is rescaled in place only when a row maximum moved.
+// One CTA per 128-row query tile.  Four warpgroups (setmaxnreg moves registers to the exp warpgroups):
+//   warp 0       TMA producer (one lane): Q once, then K (+ delta_s row) / V^T / scale atoms per KV block
+//   warp 1       MMA issuer (one lane) and owner of the tensor-memory allocation (warps 2, 3 idle)
+//   warps 4-11   exp: two warpgroups that take alternate KV blocks; thread = row with all 128 scores of the block
+//                in registers -> exp2 values, their row sum and FP4 codes of P; bound by the exp2 unit
+//   warps 12-15  stats + correction: thread = row; one block ahead of the exp warps it reads the whole S row,
+//                derives microblock maxima, running maximum, rescale factor and per-microblock constants
+//                (shared memory -> exp warps), rescales O in tensor memory when a row maximum moved, and
+//                finally writes O / l to global memory
+// S is double-buffered in tensor memory so that Q K^T and the statistics of block j+1 overlap the exp2 work
+// of block j.
 //
 // Arithmetic follows (paths inside the reference project, sageattention3_blackwell/sageattn3/blackwell/...):
 //   mainloop_tma_ws.h:509, 532-551, 865     KV blocks are walked from the last to the first
@@ -28,6 +32,17 @@
 
 namespace sage3 {
 
+// Optional per-phase cycle accounting of the first CTA (development builds only; off in the product library).
+#ifdef SAGE3_PHASE_TIMING
+#define PT_DECL long long pt_t = clock64(); long long pt_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define PT(i) { const long long pt_now = clock64(); pt_acc[i] += pt_now - pt_t; pt_t = pt_now; }
+#define PT_DUMP(slot) if (p.debug != nullptr && blockIdx.x == 0 && lane == 0) { for (int i_ = 0; i_ < 8; ++i_) p.debug[40000 + (slot) * 8 + i_] = (float)pt_acc[i_]; }
+#else
+#define PT_DECL
+#define PT(i)
+#define PT_DUMP(slot)
+#endif
+
 constexpr float kLog2Of6 = 2.584962500721156f;
 constexpr float kPScaleLog2 = -11.392317422778762f;   // log2(1 / (448 * 6)), softmax_fused.h:33
 
@@ -46,6 +61,7 @@ struct AttnParams {
 template <int D>
 struct Cfg {
     static constexpr int kStages = (D == 128) ? 6 : 8;
+    static constexpr int kThreads = 512;                      // 4 warpgroups, see the kernel
     static constexpr int kQBytes = 128 * D / 2;
     static constexpr int kSfQkBytes = (D / 64) * 512;
     static constexpr int kKBytes = 128 * D / 2;
@@ -66,9 +82,10 @@ struct Cfg {
     static constexpr int oDelta = oSfP + 2 * 1024;
     static constexpr int kDeltaPitch = 512;                   // 256 B of delta_s + 256 B that stay zero
     static constexpr int oOnes = oDelta + kStages * kDeltaPitch;   // 128 x 16 tile: column 0 = 1.0, rest 0
-    static constexpr int oMx = oOnes + 4096;                  // float [2][2][128]
-    static constexpr int oBar = oMx + 2 * 2 * 128 * 4;
-    static constexpr int kNumBars = 1 + 4 * kStages + 2 + 2 + 2 + 1 + 4;
+    static constexpr int oCst = oOnes + 4096;                 // float [2][17][128]  per block: 8 offsets, 8 scales, scaled max per row
+    static constexpr int oL = oCst + 2 * 17 * 128 * 4;        // float [2][2][128]   per exp warpgroup: row sum, scaled max it refers to
+    static constexpr int oBar = oL + 4 * 128 * 4;
+    static constexpr int kNumBars = 1 + 4 * kStages + 2 + 2 + 2 + 2 + 1 + 1 + 2 + 1;
     static constexpr int oMisc = oBar + kNumBars * 8;
     static constexpr int kSmemBytes = oMisc + 64 + 1024;      // + slack for the manual 1024-byte alignment
     // tensor-memory columns
@@ -86,11 +103,6 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) 
     __half2 v = __floats2half2_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&v);
 }
-template <typename OutT> __device__ __forceinline__ float delta_to_f(uint32_t h16);
-template <> __device__ __forceinline__ float delta_to_f<__nv_bfloat16>(uint32_t h16) { return __uint_as_float(h16 << 16); }
-template <> __device__ __forceinline__ float delta_to_f<__half>(uint32_t h16) {
-    return __half2float(__ushort_as_half(static_cast<unsigned short>(h16)));
-}
 
 // Wait executed by a whole converged warp; the verdict is made warp-uniform so that no lane leaves a loop alone.
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
@@ -98,8 +110,23 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
     return __all_sync(0xffffffffu, ok);
 }
 
+// Maxima of two 16-key microblocks held in t[0..31] (3-input max: 8 operations per 16 values, depth 3).
+__device__ __forceinline__ void microblock_max2(const float* t, float& m0, float& m1) {
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        const float* x = t + 16 * g;
+        float a = fmax3(x[0], x[1], x[2]);
+        float b = fmax3(x[3], x[4], x[5]);
+        const float c = fmax3(x[6], x[7], x[8]);
+        const float d = fmax3(x[9], x[10], x[11]);
+        a = fmax3(a, x[12], x[13]);
+        b = fmax3(b, x[14], x[15]);
+        (g ? m1 : m0) = fmax3(a, b, fmaxf(c, d));
+    }
+}
+
 template <int D, bool CAUSAL, typename OutT>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(Cfg<D>::kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
     using C = Cfg<D>;
@@ -113,7 +140,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // barriers
     auto bar = [&](int i) { return sbase + C::oBar + 8u * i; };
     const int bQ = 0, bKF = 1, bKE = bKF + S, bVF = bKE + S, bVE = bVF + S, bSF = bVE + S, bSE = bSF + 2,
-              bPF = bSE + 2, bOR = bPF + 2, bPair = bOR + 1;
+              bPF = bSE + 2, bPE = bPF + 2, bOR = bPE + 2, bOS = bOR + 1, bST = bOS + 1, bLR = bST + 2;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + C::oMisc);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + C::oMisc + 8);
 
@@ -142,12 +169,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             mbar_init(bar(bVE + i), 1);
         }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(bar(bSF + i), 1);
-            mbar_init(bar(bSE + i), 8);
-            mbar_init(bar(bPF + i), 8);
+            mbar_init(bar(bSF + i), 1);    // S buffer i holds Q K^T (+ delta_s)          (MMA commit)
+            mbar_init(bar(bSE + i), 8);    // the exp warpgroup of the block (4 warps) and the stats warps (4) have read S buffer i
+            mbar_init(bar(bST + i), 4);    // constants of the block in S buffer i are in shared memory  (stats warps)
+            mbar_init(bar(bPF + i), 4);    // P buffer i (+ its scales) is written
+            mbar_init(bar(bPE + i), 1);    // the PV MMA that read P buffer i is complete  (MMA commit)
         }
-        mbar_init(bar(bOR), 1);
-        for (int i = 0; i < 4; ++i) mbar_init(bar(bPair + i), 2);
+        mbar_init(bar(bOR), 1);            // PV of a block is complete: O is up to date  (MMA commit)
+        mbar_init(bar(bOS), 4);            // O has been rescaled for the next PV          (stats warps)
+        mbar_init(bar(bLR), 8);            // final row sums of both exp warpgroups are in shared memory
         mbar_fence_init();
     }
     {
@@ -177,8 +207,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t tmem = *tmem_slot;
 
     const float sl2 = p.sm_scale_per_head ? p.sm_scale_per_head[hq] * 1.4426950408889634f : p.sm_scale_log2;
+    float* s_cst = reinterpret_cast<float*>(sgen + C::oCst);
+    float* s_l = reinterpret_cast<float*>(sgen + C::oL);
 
-    if (warp == 0) {
+    // Register budget: 512 threads start with 128 registers each; the exp warpgroups (a whole S row per thread)
+    // take what warpgroup 0 (two single-lane roles) and the stats warpgroup do not need.
+    if (warp < 4) {
+      reg_dealloc<48>();
+      if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0 && nb > 0) {
             mbar_expect_tx(bar(bQ), C::kQBytes + C::kSfQkBytes);
@@ -188,13 +224,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const uint16_t* dptr = p.delta + ((size_t)bhq * p.nqm + drow) * ((size_t)p.nkb * kBlock);
             for (int j = 0; j < nb; ++j) {
                 const int n = nb - 1 - j, st = j % S;
-                if (j >= S && !mbar_wait(bar(bKE + st), ((j / S) - 1) & 1, abort_flag, p.status, kWaitKEmpty)) break;
+                if (j >= S && !mbar_wait<true>(bar(bKE + st), ((j / S) - 1) & 1, abort_flag, p.status, kWaitKEmpty)) break;
                 mbar_expect_tx(bar(bKF + st), C::kKBytes + C::kSfQkBytes + C::kDeltaBytes);
                 tma_load_3d(sbase + C::oK + st * 8192, &tm_k, bar(bKF + st), 0, n * kBlock, bhkv);
                 bulk_load(sbase + C::oSfK + st * 1024, p.k_sf + ((size_t)bhkv * p.nkb + n) * C::kSfQkBytes,
                           C::kSfQkBytes, bar(bKF + st));
                 bulk_load(sbase + C::oDelta + st * C::kDeltaPitch, dptr + (size_t)n * kBlock, C::kDeltaBytes, bar(bKF + st));
-                if (j >= S && !mbar_wait(bar(bVE + st), ((j / S) - 1) & 1, abort_flag, p.status, kWaitVEmpty)) break;
+                if (j >= S && !mbar_wait<true>(bar(bVE + st), ((j / S) - 1) & 1, abort_flag, p.status, kWaitVEmpty)) break;
                 mbar_expect_tx(bar(bVF + st), C::kVBytes + C::kSfVBytes);
                 tma_load_3d(sbase + C::oV + st * 8192, &tm_v, bar(bVF + st), n * 64, 0, bhkv);
                 bulk_load(sbase + C::oSfV + st * 1024, p.v_sf + ((size_t)bhkv * p.nkb + n) * C::kSfVBytes,
@@ -202,18 +238,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
+      } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0 && nb > 0) {
             constexpr uint32_t idesc_qk = make_idesc_nvfp4(128);
             constexpr uint32_t idesc_pv = make_idesc_nvfp4(D);
+            constexpr uint32_t idesc_delta = make_idesc_f16_bmn(128, std::is_same<OutT, __nv_bfloat16>::value);
             const uint64_t q_desc = make_sdesc(sbase + C::oQ, 16, C::kSboQK, C::kSwzQK);
-            constexpr uint32_t idesc_delta = make_idesc_f16_bmn(128, sizeof(OutT) == 2 && std::is_same<OutT, __nv_bfloat16>::value);
             const uint64_t ones_desc = make_sdesc(sbase + C::oOnes, 2048, 128, kSwzNone);
             auto issue_qk = [&](int j) -> bool {
                 const int st = j % S, bb = j & 1;
-                if (j >= 2 && !mbar_wait(bar(bSE + bb), ((j >> 1) - 1) & 1, abort_flag, p.status, kWaitSEmpty)) return false;
-                if (!mbar_wait(bar(bKF + st), (j / S) & 1, abort_flag, p.status, kWaitKFull)) return false;
+                if (j >= 2 && !mbar_wait<true>(bar(bSE + bb), ((j >> 1) - 1) & 1, abort_flag, p.status, kWaitSEmpty)) return false;
+                if (!mbar_wait<true>(bar(bKF + st), (j / S) & 1, abort_flag, p.status, kWaitKFull)) return false;
                 tc_fence_after();
                 const uint64_t k_desc = make_sdesc(sbase + C::oK + st * 8192, 16, C::kSboQK, C::kSwzQK);
 #pragma unroll
@@ -231,18 +267,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 tc_commit(bar(bSF + bb));
                 return true;
             };
-            bool ok = mbar_wait(bar(bQ), 0, abort_flag, p.status, kWaitQFull);
+            PT_DECL
+            bool ok = mbar_wait<true>(bar(bQ), 0, abort_flag, p.status, kWaitQFull);
             if (ok) {
 #pragma unroll
                 for (int ks = 0; ks < D / 64; ++ks)
                     tc_cp_sf(tmem + C::cSfQ + 4 * ks, make_sdesc(sbase + C::oSfQ + ks * 512, 0, 128, kSwzNone));
                 ok = issue_qk(0);
+                if (ok && nb > 1) ok = issue_qk(1);
             }
             for (int j = 0; ok && j < nb; ++j) {
                 const int st = j % S, bb = j & 1;
-                if (j + 1 < nb && !issue_qk(j + 1)) break;
-                if (!mbar_wait(bar(bVF + st), (j / S) & 1, abort_flag, p.status, kWaitVFull)) break;
-                if (!mbar_wait(bar(bPF + bb), (j >> 1) & 1, abort_flag, p.status, kWaitPFull)) break;
+                // the S buffer of block j is free as soon as the softmax warps have loaded it for their second pass
+                PT(7)
+                if (j + 2 < nb && !issue_qk(j + 2)) break;
+                PT(0)
+                if (!mbar_wait<true>(bar(bVF + st), (j / S) & 1, abort_flag, p.status, kWaitVFull)) break;
+                PT(1)
+                if (!mbar_wait<true>(bar(bPF + bb), (j >> 1) & 1, abort_flag, p.status, kWaitPFull)) break;
+                PT(2)
+                if (!mbar_wait<true>(bar(bOS), j & 1, abort_flag, p.status, kWaitOScaled)) break;
+                PT(3)
                 tc_fence_after();
                 const uint64_t p_desc = make_sdesc(sbase + C::oP + bb * C::kPBytes, 16, 512, kSwz64);
                 const uint64_t v_desc = make_sdesc(sbase + C::oV + st * 8192, 16, 512, kSwz64);
@@ -256,83 +301,81 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     tc_mma_nvfp4(tmem + C::cO, p_desc + 2 * ks, v_desc + 2 * ks, idesc_pv, tmem + C::cSfP + 4 * ks,
                                  tmem + C::cSfV + 4 * ks, (j > 0) || (ks > 0));
                 tc_commit(bar(bVE + st));
+                tc_commit(bar(bPE + bb));
                 tc_commit(bar(bOR));
+                PT(4)
             }
+            PT_DUMP(1)
         }
         __syncwarp();
-    } else {
-        // ------------------------------------------------------------------ softmax + correction + epilogue
+      }   // warps 2, 3: no role (they complete warpgroup 0 so that it can give its registers away)
+    } else if (warp < 12) {
+        reg_alloc<184>();
+        // ------------------------------------------------------------------ exp warpgroups (2 x 4 warps)
+        // Warpgroup `par` handles the blocks j = par, par + 2, ...; thread = row r with all 128 scores of the
+        // block in registers.  The block's constants (per-microblock offsets and scales, scaled running
+        // maximum) come from the stats warps through shared memory; their arrival also tells that S(j) is
+        // complete.  The two warpgroups are never
+        // synchronised with each other: the loads, waits and stores of one overlap the exp2 work of the other.
         const int quarter = warp & 3;            // tensor-memory lane quarter this warp may touch
-        const int half = (warp - 2) >> 2;        // which 64 of the 128 columns
+        const int par = (warp >> 2) - 1;         // block parity; also the S buffer and the P buffer it uses
         const int r = quarter * 32 + lane;       // row inside the tile
         const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-        float* s_mx = reinterpret_cast<float*>(sgen + C::oMx);
         const int grow = mt * kBlock + r;        // query index
-        float m_run = -INFINITY, l_run = 0.f;
+        const uint32_t s_addr = tmem + lane_addr + (par ? C::cS1 : C::cS0);
+        const float* cst = s_cst + par * (17 * 128) + r;
+        uint8_t* prow = sgen + C::oP + par * C::kPBytes + r * 64;
+        uint32_t* sfp_row = reinterpret_cast<uint32_t*>(sgen + C::oSfP + par * 1024 + (r & 31) * 16 + (r >> 5) * 4);
+        const int sw = (r >> 1) & 3;
+        const uint64_t sl2x2 = pack2f(sl2, sl2);
+        float l_run = 0.f, ms_prev = -INFINITY;
         bool alive = true;
-
-        for (int j = 0; j < nb; ++j) {
-            const int n = nb - 1 - j, bb = j & 1;
-            if (!warp_wait(bar(bSF + bb), (j >> 1) & 1, abort_flag, p.status, kWaitSFull)) { alive = false; break; }
+        PT_DECL
+        for (int j = par; j < nb; j += 2) {
+            const int n = nb - 1 - j;
+            if (!warp_wait(bar(bST + par), (j >> 1) & 1, abort_flag, p.status, kWaitStats)) { alive = false; break; }
             tc_fence_after();
-            float s[64];
-            const uint32_t s_addr = tmem + lane_addr + (bb ? C::cS1 : C::cS0) + half * 64;
-            tmem_ld32(s_addr, s);
-            tmem_ld32(s_addr + 32, s + 32);
+            float s[128];
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) tmem_ld32(s_addr + c4 * 32, s + c4 * 32);
+            float negc[8], sfv[8];
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                negc[g] = cst[g * 128];
+                sfv[g] = cst[(8 + g) * 128];
+            }
+            const float ms = cst[16 * 128];
             tc_wait_ld();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(bSE + bb));
-
-            // masks on the real key index: keys beyond Nk, and (causal) keys after the diagonal
-            const int key0 = n * kBlock + half * 64;
+            if (lane == 0) mbar_arrive(bar(bSE + par));     // S(j) is in registers, its constants are read
+            PT(4)
             const bool need_mask = ((n + 1) * kBlock > p.Nk) || (CAUSAL && (n * kBlock + kBlock - 1 > mt * kBlock + shift));
             if (need_mask) {
                 int lim = p.Nk - 1;
                 if (CAUSAL) lim = min(lim, grow + shift);
+                const int key0 = n * kBlock;
 #pragma unroll
-                for (int i = 0; i < 64; ++i)
+                for (int i = 0; i < 128; ++i)
                     if (key0 + i > lim) s[i] = -INFINITY;
             }
-            // microblock maxima and the row maximum of this block
-            float bm[4];
+            if (p.debug != nullptr && blockIdx.x == 0 && j == 0) {
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                float a = fmax3(s[16 * g], s[16 * g + 1], s[16 * g + 2]);
-#pragma unroll
-                for (int i = 3; i < 15; i += 2) a = fmax3(a, s[16 * g + i], s[16 * g + i + 1]);
-                bm[g] = fmaxf(a, s[16 * g + 15]);
+                for (int i = 0; i < 128; ++i) p.debug[r * 128 + i] = s[i];
             }
-            const float lmax = fmaxf(fmaxf(bm[0], bm[1]), fmaxf(bm[2], bm[3]));
-            s_mx[(bb * 2 + half) * 128 + r] = lmax;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(bPair + quarter));
-            if (!warp_wait(bar(bPair + quarter), j & 1, abort_flag, p.status, kWaitPair)) { alive = false; break; }
-            __syncwarp();
-            const float omax = s_mx[(bb * 2 + (half ^ 1)) * 128 + r];
-            const float m_new = fmax3(m_run, lmax, omax);
-            const bool empty = (m_new == -INFINITY);
-            const float m_cur = empty ? 0.f : m_new;
-            const float alpha = ex2_approx((m_run - m_cur) * sl2);
-            const float max_scaled = empty ? 0.f : fmaf(m_new, sl2, kPScaleLog2);
-
-            uint32_t codes[8];
-            uint32_t sfbytes = 0;
+            uint32_t codes[16];
+            uint32_t sfb[2] = {0, 0};
             float rowsum = 0.f;
-            const uint64_t sl2x2 = pack2f(sl2, sl2);
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                const bool gdead = (bm[g] == -INFINITY);
-                // E = P~ / sf = 6 * 2^((S - bm) s);   sf = max(P~) / 6 = 2^(bm s - max_scaled - log2 6)
-                const float c = gdead ? 0.f : fmaf(bm[g], sl2, -kLog2Of6);
-                const float sf = gdead ? 0.f : ex2_approx(fmaf(bm[g], sl2, -max_scaled) - kLog2Of6);
-                const uint64_t negc = pack2f(-c, -c);
+            for (int g = 0; g < 8; ++g) {
+                // E = P~ / sf = 6 * 2^((S - bm) s)  with  negc = -(bm s - log2 6)
+                const uint64_t negc2 = pack2f(negc[g], negc[g]);
                 float e[16];
                 uint64_t acc0 = 0, acc1 = 0;      // two packed partial sums (bit pattern of +0.0f pairs)
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     float a, b2;
-                    unpack2f(fma2(pack2f(s[16 * g + 2 * i], s[16 * g + 2 * i + 1]), sl2x2, negc), a, b2);
+                    unpack2f(fma2(pack2f(s[16 * g + 2 * i], s[16 * g + 2 * i + 1]), sl2x2, negc2), a, b2);
                     e[2 * i] = ex2_approx(a);
                     e[2 * i + 1] = ex2_approx(b2);
                     if (i & 1) acc1 = add2(acc1, pack2f(e[2 * i], e[2 * i + 1]));
@@ -340,77 +383,171 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 }
                 float se0, se1;
                 unpack2f(add2(acc0, acc1), se0, se1);
-                rowsum = fmaf(sf, se0 + se1, rowsum);
+                rowsum = fmaf(sfv[g], se0 + se1, rowsum);
                 codes[2 * g] = cvt_e2m1x8(e[0], e[1], e[2], e[3], e[4], e[5], e[6], e[7]);
                 codes[2 * g + 1] = cvt_e2m1x8(e[8], e[9], e[10], e[11], e[12], e[13], e[14], e[15]);
-                sfbytes |= (cvt_e4m3x2(sf, 0.f) & 0xffu) << (8 * g);
+                sfb[g >> 2] |= (cvt_e4m3x2(sfv[g], 0.f) & 0xffu) << (8 * (g & 3));
             }
-            l_run = fmaf(l_run, alpha, rowsum);
-
-            // P codes into the 64-byte-swizzled K-major tile; scales into the 128x4 atom of this column half
-            {
-                uint8_t* prow = sgen + C::oP + bb * C::kPBytes + r * 64;
-                const int sw = (r >> 1) & 3;
-                *reinterpret_cast<uint4*>(prow + (((2 * half) ^ sw) << 4)) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
-                *reinterpret_cast<uint4*>(prow + (((2 * half + 1) ^ sw) << 4)) = make_uint4(codes[4], codes[5], codes[6], codes[7]);
-                *reinterpret_cast<uint32_t*>(sgen + C::oSfP + bb * 1024 + half * 512 + (r & 31) * 16 + (r >> 5) * 4) = sfbytes;
-            }
-            if (p.debug != nullptr && blockIdx.x == 0 && j == 0) {
+            // row sum relative to the running maximum of this block: rescale what this warpgroup has so far
+            const float a_eff = (l_run == 0.f) ? 0.f : ex2_approx(ms_prev - ms);
+            l_run = fmaf(l_run, a_eff, rowsum);
+            ms_prev = ms;
+            if (p.debug != nullptr && blockIdx.x == 0 && j == 0) p.debug[16384 + 128 + r] = rowsum;
+            PT(0)
+            // P buffer `par` was last read by the PV MMA of block j - 2
+            if (j >= 2 && !warp_wait(bar(bPE + par), ((j >> 1) - 1) & 1, abort_flag, p.status, kWaitPEmpty)) { alive = false; break; }
+            // P codes: four 16-byte chunks of the 64-byte-swizzled K-major row; scales: one word per 64-key atom
 #pragma unroll
-                for (int i = 0; i < 64; ++i) p.debug[r * 128 + half * 64 + i] = s[i];
-                if (half == 0) { p.debug[16384 + r] = m_new; }
-                p.debug[16384 + 128 + half * 128 + r] = rowsum;
+            for (int c = 0; c < 4; ++c)
+                *reinterpret_cast<uint4*>(prow + ((c ^ sw) << 4)) =
+                    make_uint4(codes[4 * c], codes[4 * c + 1], codes[4 * c + 2], codes[4 * c + 3]);
+            sfp_row[0] = sfb[0];
+            sfp_row[128] = sfb[1];
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(bPF + par));
+            PT(3)
+        }
+        PT_DUMP(warp)
+        // hand the row sum (and the scaled maximum it refers to) to the stats warps
+        if (alive && nb > 0) {
+            s_l[par * 256 + r] = l_run;
+            s_l[par * 256 + 128 + r] = ms_prev;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(bLR));
+        }
+        __syncwarp();
+    } else {
+        reg_dealloc<96>();
+        // ------------------------------------------------------------------ stats + correction + epilogue (4 warps)
+        // Thread = row r.  For every block, ahead of the exp warps: microblock maxima of the whole row, running
+        // maximum, rescale factor and the per-microblock constants, published through shared memory.  Then O is
+        // multiplied by the rescale factor before the block's PV MMA (only when some row of the warp moved its
+        // maximum).  At the end O / l goes to global memory.
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+        const int grow = mt * kBlock + r;
+        float m_run = -INFINITY;
+        bool alive = true;
+        PT_DECL
+        // statistics of block j: constants into shared memory, rescale factor returned
+        auto do_stats = [&](int j, float& alpha_out) -> bool {
+            const int n = nb - 1 - j, bb = j & 1;
+            if (!warp_wait(bar(bSF + bb), (j >> 1) & 1, abort_flag, p.status, kWaitSFull)) return false;
+            PT(0)
+            tc_fence_after();
+            const bool need_mask = ((n + 1) * kBlock > p.Nk) || (CAUSAL && (n * kBlock + kBlock - 1 > mt * kBlock + shift));
+            int lim = p.Nk - 1;
+            if (CAUSAL) lim = min(lim, grow + shift);
+            auto mask32 = [&](float* t, int c4) {
+                const int key0 = n * kBlock + c4 * 32;
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (key0 + i > lim) t[i] = -INFINITY;
+            };
+            const uint32_t sa = tmem + lane_addr + (bb ? C::cS1 : C::cS0);
+            float bm[8];
+            float t0[32], t1[32];
+            // two loads in flight at a time
+            tmem_ld32(sa, t0);
+            tmem_ld32(sa + 32, t1);
+            tc_wait_ld();
+            if (need_mask) { mask32(t0, 0); mask32(t1, 1); }
+            microblock_max2(t0, bm[0], bm[1]);
+            microblock_max2(t1, bm[2], bm[3]);
+            tmem_ld32(sa + 64, t0);
+            tmem_ld32(sa + 96, t1);
+            tc_wait_ld();
+            if (need_mask) { mask32(t0, 2); mask32(t1, 3); }
+            microblock_max2(t0, bm[4], bm[5]);
+            microblock_max2(t1, bm[6], bm[7]);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(bSE + bb));
+            PT(1)
+            const float m_new = fmaxf(fmax3(m_run, bm[0], bm[1]), fmaxf(fmax3(bm[2], bm[3], bm[4]), fmax3(bm[5], bm[6], bm[7])));
+            const bool empty = (m_new == -INFINITY);
+            const float m_cur = empty ? 0.f : m_new;
+            alpha_out = ex2_approx((m_run - m_cur) * sl2);        // m_run = -inf  ->  0
+            const float max_scaled = empty ? 0.f : fmaf(m_new, sl2, kPScaleLog2);
+            float* cst = s_cst + bb * (17 * 128);
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                const bool gdead = (bm[g] == -INFINITY);
+                // sf = max(P~) / 6 = 2^(bm s - max_scaled - log2 6);  negc = -(bm s - log2 6)
+                cst[g * 128 + r] = gdead ? 0.f : -fmaf(bm[g], sl2, -kLog2Of6);
+                cst[(8 + g) * 128 + r] = gdead ? 0.f : ex2_approx(fmaf(bm[g], sl2, -max_scaled) - kLog2Of6);
             }
-            // O of the previous block must be complete before it is rescaled / before P of block j-2 is reused
+            cst[16 * 128 + r] = m_cur * sl2;      // scaled running maximum the exp2 values of this block refer to
+            m_run = m_new;
+            if (p.debug != nullptr && blockIdx.x == 0 && j == 0) p.debug[16384 + r] = m_new;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(bST + bb));
+            PT(2)
+            return true;
+        };
+        float alpha = 1.f;
+        if (nb > 0) alive = do_stats(0, alpha);
+        for (int j = 0; alive && j < nb; ++j) {
+            // statistics run one block ahead of the rescaling, so the exp warps never wait for a PV MMA
+            float alpha_next = 1.f;
+            if (j + 1 < nb && !do_stats(j + 1, alpha_next)) { alive = false; break; }
             if (j > 0) {
                 if (!warp_wait(bar(bOR), (j - 1) & 1, abort_flag, p.status, kWaitOReady)) { alive = false; break; }
+                PT(3)
                 if (__any_sync(0xffffffffu, alpha != 1.0f)) {
                     tc_fence_after();
+                    const uint64_t a2 = pack2f(alpha, alpha);
 #pragma unroll
                     for (int cc = 0; cc < D / 64; ++cc) {
-                        float o[32];
-                        const uint32_t o_addr = tmem + lane_addr + C::cO + half * (D / 2) + cc * 32;
-                        tmem_ld32(o_addr, o);
+                        float o0[32], o1[32];
+                        const uint32_t o_addr = tmem + lane_addr + C::cO + cc * 64;
+                        tmem_ld32(o_addr, o0);
+                        tmem_ld32(o_addr + 32, o1);
                         tc_wait_ld();
-                        const uint64_t a2 = pack2f(alpha, alpha);
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) unpack2f(mul2(pack2f(o[2 * i], o[2 * i + 1]), a2), o[2 * i], o[2 * i + 1]);
-                        tmem_st32(o_addr, o);
+                        for (int i = 0; i < 16; ++i) {
+                            unpack2f(mul2(pack2f(o0[2 * i], o0[2 * i + 1]), a2), o0[2 * i], o0[2 * i + 1]);
+                            unpack2f(mul2(pack2f(o1[2 * i], o1[2 * i + 1]), a2), o1[2 * i], o1[2 * i + 1]);
+                        }
+                        tmem_st32(o_addr, o0);
+                        tmem_st32(o_addr + 32, o1);
                     }
                     tc_wait_st();
                 }
             }
-            fence_proxy_async_smem();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(bPF + bb));
-            m_run = m_new;
+            if (lane == 0) mbar_arrive(bar(bOS));
+            alpha = alpha_next;
+            PT(4)
         }
-
-        // ------------------------------------------------------------------ epilogue
+        PT_DUMP(warp)
         if (alive && !dead_launch) {
             float l_tot = 0.f;
             if (nb > 0) {
-                alive = warp_wait(bar(bOR), (nb - 1) & 1, abort_flag, p.status, kWaitOReady);
+                alive = warp_wait(bar(bLR), 0, abort_flag, p.status, kWaitAlpha);
+                if (alive) alive = warp_wait(bar(bOR), (nb - 1) & 1, abort_flag, p.status, kWaitOReady);
                 if (alive) {
                     tc_fence_after();
-                    const int bb = nb & 1;
-                    s_mx[(bb * 2 + half) * 128 + r] = l_run;
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(bPair + quarter));
-                    alive = warp_wait(bar(bPair + quarter), nb & 1, abort_flag, p.status, kWaitPair);
-                    __syncwarp();
-                    if (alive) l_tot = l_run + s_mx[(bb * 2 + (half ^ 1)) * 128 + r];
+                    // each exp warpgroup's sum refers to the maximum of its own last block: bring both to the final one
+                    const float ms_final = (m_run == -INFINITY ? 0.f : m_run) * sl2;
+#pragma unroll
+                    for (int w2 = 0; w2 < 2; ++w2) {
+                        const float lw = s_l[w2 * 256 + r], lm = s_l[w2 * 256 + 128 + r];
+                        if (lw != 0.f) l_tot += lw * ex2_approx(lm - ms_final);
+                    }
                 }
             }
             if (alive) {
                 const float inv_l = (l_tot == 0.f || l_tot != l_tot) ? 0.f : __frcp_rn(l_tot);
-                OutT* orow = static_cast<OutT*>(p.out) + b * p.os0 + hq * p.os1 + (int64_t)grow * p.os2 + half * (D / 2);
+                OutT* orow = static_cast<OutT*>(p.out) + b * p.os0 + hq * p.os1 + (int64_t)grow * p.os2;
 #pragma unroll
-                for (int cc = 0; cc < D / 64; ++cc) {
+                for (int cc = 0; cc < D / 32; ++cc) {
                     float o[32];
                     if (nb > 0) {
-                        tmem_ld32(tmem + lane_addr + C::cO + half * (D / 2) + cc * 32, o);
+                        tmem_ld32(tmem + lane_addr + C::cO + cc * 32, o);
                         tc_wait_ld();
                     } else {
 #pragma unroll
@@ -418,8 +555,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     }
                     if (p.debug != nullptr && blockIdx.x == 0) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) p.debug[16384 + 512 + r * D + half * (D / 2) + cc * 32 + i] = o[i];
-                        if (half == 0 && cc == 0) p.debug[16384 + 384 + r] = l_tot;
+                        for (int i = 0; i < 32; ++i) p.debug[16384 + 512 + r * D + cc * 32 + i] = o[i];
+                        if (cc == 0) p.debug[16384 + 384 + r] = l_tot;
                     }
                     if (grow < p.Nq) {
 #pragma unroll
@@ -490,7 +627,7 @@ static cudaError_t launch_t(const AttnArgs& a, const CUtensorMap& tq, const CUte
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes);
     if (e != cudaSuccess) return e;
     const int grid = a.B * a.Hq * (a.Nq_p / kBlock);
-    kern<<<grid, 320, Cfg<D>::kSmemBytes, st>>>(tq, tk, tv, p);
+    kern<<<grid, Cfg<D>::kThreads, Cfg<D>::kSmemBytes, st>>>(tq, tk, tv, p);
     return cudaGetLastError();
 }
 

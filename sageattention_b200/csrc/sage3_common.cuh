@@ -16,7 +16,7 @@ constexpr int kMicro = 16;    // NVFP4 microblock
 enum : int {
     kWaitQFull = 101, kWaitKFull = 102, kWaitVFull = 103, kWaitKEmpty = 104, kWaitVEmpty = 105,
     kWaitSFull = 106, kWaitSEmpty = 107, kWaitPFull = 108, kWaitOReady = 109, kWaitPair = 110,
-    kWaitDelta = 111
+    kWaitDelta = 111, kWaitOScaled = 112, kWaitPEmpty = 113, kWaitAlpha = 114, kWaitStats = 115
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -47,6 +47,10 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
     return r;
 }
+
+// per-warpgroup register budget (all four warps of a warpgroup execute the same call)
+template <int N> __device__ __forceinline__ void reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_dealloc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 // packed fp32 pairs (one issue slot for two lanes of math)
 __device__ __forceinline__ uint64_t pack2f(float lo, float hi) {
@@ -148,6 +152,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // the caller must then leave its loop.  Nothing ever spins without a limit.
 constexpr long long kWaitLimitCycles = 2000000000LL;   // about a second
 
+// kBackoff: sleep a little between polls (single-lane roles, so that polling does not take issue slots
+// from the math warps of the same scheduler).
+template <bool kBackoff = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status_word, int code) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -155,6 +162,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     uint32_t spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (kBackoff) __nanosleep(40);
         if ((++spins & 0x3f) == 0) {
             if (*abort_flag != 0) return false;
             if (clock64() - t0 > kWaitLimitCycles || *reinterpret_cast<volatile int*>(status_word) != 0) {
