@@ -3,7 +3,8 @@
 //
 // One CTA per 128-row query tile.  Four warpgroups (setmaxnreg moves registers to the exp warpgroups):
 //   warp 0       TMA producer (one lane): Q once, then K (+ delta_s row) / V^T / scale atoms per KV block
-//   warp 1       MMA issuer (one lane) and owner of the tensor-memory allocation (warps 2, 3 idle)
+//   warp 1       Q K^T MMA issuer (one lane) and owner of the tensor-memory allocation
+//   warp 2       P V MMA issuer (one lane); warp 3 idle
 //   warps 4-11   exp: two warpgroups that take alternate KV blocks; thread = row with all 128 scores of the block
 //                in registers -> exp2 values, their row sum and FP4 codes of P; bound by the exp2 unit
 //   warps 12-15  stats + correction: thread = row; one block ahead of the exp warps it reads the whole S row,
@@ -239,17 +240,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         __syncwarp();
       } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
+        // ------------------------------------------------------------------ Q K^T MMA issuer
         if (lane == 0 && nb > 0) {
             constexpr uint32_t idesc_qk = make_idesc_nvfp4(128);
-            constexpr uint32_t idesc_pv = make_idesc_nvfp4(D);
             constexpr uint32_t idesc_delta = make_idesc_f16_bmn(128, std::is_same<OutT, __nv_bfloat16>::value);
             const uint64_t q_desc = make_sdesc(sbase + C::oQ, 16, C::kSboQK, C::kSwzQK);
             const uint64_t ones_desc = make_sdesc(sbase + C::oOnes, 2048, 128, kSwzNone);
             auto issue_qk = [&](int j) -> bool {
                 const int st = j % S, bb = j & 1;
-                if (j >= 2 && !mbar_wait<true>(bar(bSE + bb), ((j >> 1) - 1) & 1, abort_flag, p.status, kWaitSEmpty)) return false;
-                if (!mbar_wait<true>(bar(bKF + st), (j / S) & 1, abort_flag, p.status, kWaitKFull)) return false;
+                if (j >= 2 && !mbar_wait(bar(bSE + bb), ((j >> 1) - 1) & 1, abort_flag, p.status, kWaitSEmpty)) return false;
+                if (!mbar_wait(bar(bKF + st), (j / S) & 1, abort_flag, p.status, kWaitKFull)) return false;
                 tc_fence_after();
                 const uint64_t k_desc = make_sdesc(sbase + C::oK + st * 8192, 16, C::kSboQK, C::kSwzQK);
 #pragma unroll
@@ -268,25 +268,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 return true;
             };
             PT_DECL
-            bool ok = mbar_wait<true>(bar(bQ), 0, abort_flag, p.status, kWaitQFull);
+            bool ok = mbar_wait(bar(bQ), 0, abort_flag, p.status, kWaitQFull);
             if (ok) {
 #pragma unroll
                 for (int ks = 0; ks < D / 64; ++ks)
                     tc_cp_sf(tmem + C::cSfQ + 4 * ks, make_sdesc(sbase + C::oSfQ + ks * 512, 0, 128, kSwzNone));
-                ok = issue_qk(0);
-                if (ok && nb > 1) ok = issue_qk(1);
             }
+            // S buffer j & 1 is free as soon as block j - 2 sits in the registers of its exp and stats warps
             for (int j = 0; ok && j < nb; ++j) {
-                const int st = j % S, bb = j & 1;
-                // the S buffer of block j is free as soon as the softmax warps have loaded it for their second pass
-                PT(7)
-                if (j + 2 < nb && !issue_qk(j + 2)) break;
+                ok = issue_qk(j);
                 PT(0)
-                if (!mbar_wait<true>(bar(bVF + st), (j / S) & 1, abort_flag, p.status, kWaitVFull)) break;
+            }
+            PT_DUMP(1)
+        }
+        __syncwarp();
+      } else if (warp == 2) {
+        // ------------------------------------------------------------------ PV MMA issuer
+        if (lane == 0 && nb > 0) {
+            constexpr uint32_t idesc_pv = make_idesc_nvfp4(D);
+            PT_DECL
+            for (int j = 0; j < nb; ++j) {
+                const int st = j % S, bb = j & 1;
+                if (!mbar_wait(bar(bVF + st), (j / S) & 1, abort_flag, p.status, kWaitVFull)) break;
                 PT(1)
-                if (!mbar_wait<true>(bar(bPF + bb), (j >> 1) & 1, abort_flag, p.status, kWaitPFull)) break;
+                if (!mbar_wait(bar(bPF + bb), (j >> 1) & 1, abort_flag, p.status, kWaitPFull)) break;
                 PT(2)
-                if (!mbar_wait<true>(bar(bOS), j & 1, abort_flag, p.status, kWaitOScaled)) break;
+                if (!mbar_wait(bar(bOS), j & 1, abort_flag, p.status, kWaitOScaled)) break;
                 PT(3)
                 tc_fence_after();
                 const uint64_t p_desc = make_sdesc(sbase + C::oP + bb * C::kPBytes, 16, 512, kSwz64);
@@ -305,10 +312,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 tc_commit(bar(bOR));
                 PT(4)
             }
-            PT_DUMP(1)
+            PT_DUMP(2)
         }
         __syncwarp();
-      }   // warps 2, 3: no role (they complete warpgroup 0 so that it can give its registers away)
+      }   // warp 3: no role (it completes warpgroup 0 so that it can give its registers away)
     } else if (warp < 12) {
         reg_alloc<184>();
         // ------------------------------------------------------------------ exp warpgroups (2 x 4 warps)
