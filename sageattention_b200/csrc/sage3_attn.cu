@@ -5,15 +5,14 @@
 //   warp 0       TMA producer (one lane): Q once, then K (+ delta_s row) / V^T / scale atoms per KV block
 //   warp 1       Q K^T MMA issuer (one lane) and owner of the tensor-memory allocation
 //   warp 2       P V MMA issuer (one lane); warp 3 idle
-//   warps 4-11   softmax: two warpgroups that take alternate KV blocks; thread = row with all 128 scores of the
-//                block in registers -> microblock maxima, running maximum (handed from one warpgroup to the
-//                other through shared memory), exp2 values, their row sum and FP4 codes of P
-//   warps 12-15  correction: thread = row; rescales O in tensor memory when a row maximum moved, and finally
-//                writes O / l to global memory
-// While one softmax warpgroup works on block j the other works on block j+1, so the loads, waits and stores of
-// one overlap the exp2 work of the other.  S needs a single buffer in tensor memory (it moves to registers at
-// once).  Each warpgroup accumulates its blocks into its own O accumulator, so the rescale -> P V chain of one
-// accumulator has two block periods of slack; the two accumulators are merged in the epilogue.
+//   warps 4-11   exp: two warpgroups that take alternate KV blocks; thread = row with all 128 scores of the block
+//                in registers -> exp2 values, their row sum and FP4 codes of P; bound by the exp2 unit
+//   warps 12-15  stats + correction: thread = row; one block ahead of the exp warps it reads the whole S row,
+//                derives microblock maxima, running maximum, rescale factor and per-microblock constants
+//                (shared memory -> exp warps), rescales O in tensor memory when a row maximum moved, and
+//                finally writes O / l to global memory
+// S is double-buffered in tensor memory so that Q K^T and the statistics of block j+1 overlap the exp2 work
+// of block j.
 //
 // Arithmetic follows (paths inside the reference project, sageattention3_blackwell/sageattn3/blackwell/...):
 //   mainloop_tma_ws.h:509, 532-551, 865     KV blocks are walked from the last to the first
@@ -84,16 +83,14 @@ struct Cfg {
     static constexpr int oDelta = oSfP + 2 * 1024;
     static constexpr int kDeltaPitch = 512;                   // 256 B of delta_s + 256 B that stay zero
     static constexpr int oOnes = oDelta + kStages * kDeltaPitch;   // 128 x 16 tile: column 0 = 1.0, rest 0
-    static constexpr int oMx = oOnes + 4096;                  // float [2][128]      running maximum after the last block of each exp warpgroup
-    static constexpr int oAlpha = oMx + 2 * 128 * 4;          // float [4][128]      rescale factor per row, 4 blocks deep
-    static constexpr int oL = oAlpha + 4 * 128 * 4;        // float [2][2][128]   per exp warpgroup: row sum, scaled max it refers to
+    static constexpr int oCst = oOnes + 4096;                 // float [2][17][128]  per block: 8 offsets, 8 scales, scaled max per row
+    static constexpr int oL = oCst + 2 * 17 * 128 * 4;        // float [2][2][128]   per exp warpgroup: row sum, scaled max it refers to
     static constexpr int oBar = oL + 4 * 128 * 4;
-    static constexpr int kNumBars = 1 + 4 * kStages + 1 + 2 + 2 + 4 + 8 + 1;
+    static constexpr int kNumBars = 1 + 4 * kStages + 2 + 2 + 2 + 2 + 1 + 1 + 2 + 1;
     static constexpr int oMisc = oBar + kNumBars * 8;
     static constexpr int kSmemBytes = oMisc + 64 + 1024;      // + slack for the manual 1024-byte alignment
     // tensor-memory columns
-    // S (single buffer: it is copied to registers at once), one O accumulator per softmax warpgroup, scale factors
-    static constexpr uint32_t cS = 0, cO0 = 128, cO1 = 256, cSfQ = 384, cSfK = 392, cSfP = 400, cSfV = 408;
+    static constexpr uint32_t cS0 = 0, cS1 = 128, cO = 256, cSfQ = 384, cSfK = 392, cSfP = 400, cSfV = 408;
     static constexpr uint64_t kSwzQK = (D == 128) ? kSwz64 : kSwz32;
     static constexpr uint32_t kSboQK = (D == 128) ? 512 : 256;
 };
@@ -143,8 +140,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
     // barriers
     auto bar = [&](int i) { return sbase + C::oBar + 8u * i; };
-    const int bQ = 0, bKF = 1, bQK = bKF + S, bVF = bQK + S, bPV = bVF + S, bSE = bPV + S, bPF = bSE + 1,
-              bOS = bPF + 2, bAR = bOS + 2, bMX = bAR + 4, bLR = bMX + 8;
+    const int bQ = 0, bKF = 1, bKE = bKF + S, bVF = bKE + S, bVE = bVF + S, bSF = bVE + S, bSE = bSF + 2,
+              bPF = bSE + 2, bPE = bPF + 2, bOR = bPE + 2, bOS = bOR + 1, bST = bOS + 1, bLR = bST + 2;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + C::oMisc);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + C::oMisc + 8);
 
@@ -168,17 +165,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mbar_init(bar(bQ), 1);
         for (int i = 0; i < S; ++i) {
             mbar_init(bar(bKF + i), 1);
-            mbar_init(bar(bQK + i), 1);    // Q K^T (+ delta_s) of the block in stage i is complete: S is full, the K stage is free
+            mbar_init(bar(bKE + i), 1);
             mbar_init(bar(bVF + i), 1);
-            mbar_init(bar(bPV + i), 1);    // P V of the block in stage i is complete: O is up to date, V stage and P buffer are free
+            mbar_init(bar(bVE + i), 1);
         }
         for (int i = 0; i < 2; ++i) {
+            mbar_init(bar(bSF + i), 1);    // S buffer i holds Q K^T (+ delta_s)          (MMA commit)
+            mbar_init(bar(bSE + i), 8);    // the exp warpgroup of the block (4 warps) and the stats warps (4) have read S buffer i
+            mbar_init(bar(bST + i), 4);    // constants of the block in S buffer i are in shared memory  (stats warps)
             mbar_init(bar(bPF + i), 4);    // P buffer i (+ its scales) is written
+            mbar_init(bar(bPE + i), 1);    // the PV MMA that read P buffer i is complete  (MMA commit)
         }
-        mbar_init(bar(bSE), 4);            // the softmax warpgroup of the block has S in registers
-        for (int i = 0; i < 2; ++i) mbar_init(bar(bOS + i), 4);    // O accumulator i has been rescaled for its next PV (correction warps)
-        for (int i = 0; i < 4; ++i) mbar_init(bar(bAR + i), 4);    // rescale factors of block i mod 4 are in shared memory
-        for (int i = 0; i < 8; ++i) mbar_init(bar(bMX + i), 1);    // [warpgroup][row quarter]: running maximum published
+        mbar_init(bar(bOR), 1);            // PV of a block is complete: O is up to date  (MMA commit)
+        mbar_init(bar(bOS), 4);            // O has been rescaled for the next PV          (stats warps)
         mbar_init(bar(bLR), 8);            // final row sums of both exp warpgroups are in shared memory
         mbar_fence_init();
     }
@@ -209,14 +208,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t tmem = *tmem_slot;
 
     const float sl2 = p.sm_scale_per_head ? p.sm_scale_per_head[hq] * 1.4426950408889634f : p.sm_scale_log2;
-    float* s_mx = reinterpret_cast<float*>(sgen + C::oMx);
-    float* s_alpha = reinterpret_cast<float*>(sgen + C::oAlpha);
+    float* s_cst = reinterpret_cast<float*>(sgen + C::oCst);
     float* s_l = reinterpret_cast<float*>(sgen + C::oL);
 
     // Register budget: 512 threads start with 128 registers each; the exp warpgroups (a whole S row per thread)
     // take what warpgroup 0 (two single-lane roles) and the stats warpgroup do not need.
     if (warp < 4) {
-      reg_dealloc<32>();
+      reg_dealloc<48>();
       if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0 && nb > 0) {
@@ -227,13 +225,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const uint16_t* dptr = p.delta + ((size_t)bhq * p.nqm + drow) * ((size_t)p.nkb * kBlock);
             for (int j = 0; j < nb; ++j) {
                 const int n = nb - 1 - j, st = j % S;
-                if (j >= S && !mbar_wait<true>(bar(bQK + st), ((j / S) - 1) & 1, abort_flag, p.status, kWaitKEmpty)) break;
+                if (j >= S && !mbar_wait<true>(bar(bKE + st), ((j / S) - 1) & 1, abort_flag, p.status, kWaitKEmpty)) break;
                 mbar_expect_tx(bar(bKF + st), C::kKBytes + C::kSfQkBytes + C::kDeltaBytes);
                 tma_load_3d(sbase + C::oK + st * 8192, &tm_k, bar(bKF + st), 0, n * kBlock, bhkv);
                 bulk_load(sbase + C::oSfK + st * 1024, p.k_sf + ((size_t)bhkv * p.nkb + n) * C::kSfQkBytes,
                           C::kSfQkBytes, bar(bKF + st));
                 bulk_load(sbase + C::oDelta + st * C::kDeltaPitch, dptr + (size_t)n * kBlock, C::kDeltaBytes, bar(bKF + st));
-                if (j >= S && !mbar_wait<true>(bar(bPV + st), ((j / S) - 1) & 1, abort_flag, p.status, kWaitVEmpty)) break;
+                if (j >= S && !mbar_wait<true>(bar(bVE + st), ((j / S) - 1) & 1, abort_flag, p.status, kWaitVEmpty)) break;
                 mbar_expect_tx(bar(bVF + st), C::kVBytes + C::kSfVBytes);
                 tma_load_3d(sbase + C::oV + st * 8192, &tm_v, bar(bVF + st), n * 64, 0, bhkv);
                 bulk_load(sbase + C::oSfV + st * 1024, p.v_sf + ((size_t)bhkv * p.nkb + n) * C::kSfVBytes,
@@ -249,8 +247,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const uint64_t q_desc = make_sdesc(sbase + C::oQ, 16, C::kSboQK, C::kSwzQK);
             const uint64_t ones_desc = make_sdesc(sbase + C::oOnes, 2048, 128, kSwzNone);
             auto issue_qk = [&](int j) -> bool {
-                const int st = j % S;
-                if (j >= 1 && !mbar_wait(bar(bSE), (j - 1) & 1, abort_flag, p.status, kWaitSEmpty)) return false;
+                const int st = j % S, bb = j & 1;
+                if (j >= 2 && !mbar_wait(bar(bSE + bb), ((j >> 1) - 1) & 1, abort_flag, p.status, kWaitSEmpty)) return false;
                 if (!mbar_wait(bar(bKF + st), (j / S) & 1, abort_flag, p.status, kWaitKFull)) return false;
                 tc_fence_after();
                 const uint64_t k_desc = make_sdesc(sbase + C::oK + st * 8192, 16, C::kSboQK, C::kSwzQK);
@@ -259,13 +257,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     tc_cp_sf(tmem + C::cSfK + 4 * ks, make_sdesc(sbase + C::oSfK + st * 1024 + ks * 512, 0, 128, kSwzNone));
                 // S <- 1 (x) delta_s: A = [128 x 16] with ones in column 0 (K-major), B = the delta_s row read as an
                 // MN-major [16 x 128] operand whose rows 1..15 alias finite data and meet zeros in A
-                tc_mma_f16(tmem + C::cS, ones_desc,
+                tc_mma_f16(tmem + (bb ? C::cS1 : C::cS0), ones_desc,
                            make_sdesc(sbase + C::oDelta + st * C::kDeltaPitch, 16, 16, kSwzNone), idesc_delta, false);
 #pragma unroll
                 for (int ks = 0; ks < D / 64; ++ks)
-                    tc_mma_nvfp4(tmem + C::cS, q_desc + 2 * ks, k_desc + 2 * ks, idesc_qk,
+                    tc_mma_nvfp4(tmem + (bb ? C::cS1 : C::cS0), q_desc + 2 * ks, k_desc + 2 * ks, idesc_qk,
                                  tmem + C::cSfQ + 4 * ks, tmem + C::cSfK + 4 * ks, true);
-                tc_commit(bar(bQK + st));
+                tc_commit(bar(bKE + st));
+                tc_commit(bar(bSF + bb));
                 return true;
             };
             PT_DECL
@@ -294,7 +293,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 PT(1)
                 if (!mbar_wait(bar(bPF + bb), (j >> 1) & 1, abort_flag, p.status, kWaitPFull)) break;
                 PT(2)
-                if (!mbar_wait(bar(bOS + bb), (j >> 1) & 1, abort_flag, p.status, kWaitOScaled)) break;
+                if (!mbar_wait(bar(bOS), j & 1, abort_flag, p.status, kWaitOScaled)) break;
                 PT(3)
                 tc_fence_after();
                 const uint64_t p_desc = make_sdesc(sbase + C::oP + bb * C::kPBytes, 16, 512, kSwz64);
@@ -306,9 +305,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 }
 #pragma unroll
                 for (int ks = 0; ks < 2; ++ks)
-                    tc_mma_nvfp4(tmem + (bb ? C::cO1 : C::cO0), p_desc + 2 * ks, v_desc + 2 * ks, idesc_pv,
-                                 tmem + C::cSfP + 4 * ks, tmem + C::cSfV + 4 * ks, (j > 1) || (ks > 0));
-                tc_commit(bar(bPV + st));
+                    tc_mma_nvfp4(tmem + C::cO, p_desc + 2 * ks, v_desc + 2 * ks, idesc_pv, tmem + C::cSfP + 4 * ks,
+                                 tmem + C::cSfV + 4 * ks, (j > 0) || (ks > 0));
+                tc_commit(bar(bVE + st));
+                tc_commit(bar(bPE + bb));
+                tc_commit(bar(bOR));
                 PT(4)
             }
             PT_DUMP(2)
@@ -316,18 +317,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         __syncwarp();
       }   // warp 3: no role (it completes warpgroup 0 so that it can give its registers away)
     } else if (warp < 12) {
-        reg_alloc<200>();
-        // ------------------------------------------------------------------ softmax warpgroups (2 x 4 warps)
+        reg_alloc<184>();
+        // ------------------------------------------------------------------ exp warpgroups (2 x 4 warps)
         // Warpgroup `par` handles the blocks j = par, par + 2, ...; thread = row r with all 128 scores of the
-        // block in registers.  The only coupling between the two warpgroups is the running row maximum,
-        // which each publishes right after its max pass.  Otherwise they are never
+        // block in registers.  The block's constants (per-microblock offsets and scales, scaled running
+        // maximum) come from the stats warps through shared memory; their arrival also tells that S(j) is
+        // complete.  The two warpgroups are never
         // synchronised with each other: the loads, waits and stores of one overlap the exp2 work of the other.
         const int quarter = warp & 3;            // tensor-memory lane quarter this warp may touch
         const int par = (warp >> 2) - 1;         // block parity; also the S buffer and the P buffer it uses
         const int r = quarter * 32 + lane;       // row inside the tile
         const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
         const int grow = mt * kBlock + r;        // query index
-        const uint32_t s_addr = tmem + lane_addr + C::cS;
+        const uint32_t s_addr = tmem + lane_addr + (par ? C::cS1 : C::cS0);
+        const float* cst = s_cst + par * (17 * 128) + r;
         uint8_t* prow = sgen + C::oP + par * C::kPBytes + r * 64;
         uint32_t* sfp_row = reinterpret_cast<uint32_t*>(sgen + C::oSfP + par * 1024 + (r & 31) * 16 + (r >> 5) * 4);
         const int sw = (r >> 1) & 3;
@@ -337,15 +340,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         PT_DECL
         for (int j = par; j < nb; j += 2) {
             const int n = nb - 1 - j;
-            if (!warp_wait(bar(bQK + j % S), (j / S) & 1, abort_flag, p.status, kWaitSFull)) { alive = false; break; }
+            if (!warp_wait(bar(bST + par), (j >> 1) & 1, abort_flag, p.status, kWaitStats)) { alive = false; break; }
             tc_fence_after();
             float s[128];
 #pragma unroll
             for (int c4 = 0; c4 < 4; ++c4) tmem_ld32(s_addr + c4 * 32, s + c4 * 32);
+            float negc[8], sfv[8];
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                negc[g] = cst[g * 128];
+                sfv[g] = cst[(8 + g) * 128];
+            }
+            const float ms = cst[16 * 128];
             tc_wait_ld();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(bSE));           // S(j) is in registers: the buffer may take block j + 1
+            if (lane == 0) mbar_arrive(bar(bSE + par));     // S(j) is in registers, its constants are read
             PT(4)
             const bool need_mask = ((n + 1) * kBlock > p.Nk) || (CAUSAL && (n * kBlock + kBlock - 1 > mt * kBlock + shift));
             if (need_mask) {
@@ -360,49 +370,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
                 for (int i = 0; i < 128; ++i) p.debug[r * 128 + i] = s[i];
             }
-            // microblock maxima and the block's row maximum
-            float bm[8];
-#pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) microblock_max2(s + 32 * c4, bm[2 * c4], bm[2 * c4 + 1]);
-            const float lmax = fmaxf(fmax3(bm[0], bm[1], bm[2]), fmaxf(fmax3(bm[3], bm[4], bm[5]), fmaxf(bm[6], bm[7])));
-            PT(5)
-            // running maximum after the previous block: kept by the other warpgroup
-            float m_prev = -INFINITY;
-            if (j > 0) {
-                const uint32_t par_prev = par ? ((j >> 1) & 1) : (((j >> 1) - 1) & 1);
-                if (!warp_wait(bar(bMX + (par ^ 1) * 4 + quarter), par_prev, abort_flag, p.status, kWaitPair)) { alive = false; break; }
-                m_prev = s_mx[(par ^ 1) * 128 + r];
-            }
-            PT(6)
-            const float m_new = fmaxf(m_prev, lmax);
-            const bool empty = (m_new == -INFINITY);
-            const float m_cur = empty ? 0.f : m_new;
-            s_mx[par * 128 + r] = m_new;
-            // this warpgroup's accumulators (row sum here, O in tensor memory) refer to the maximum of its previous
-            // block: factor that brings them to the maximum of this one (nothing accumulated yet -> 0)
-            const float ms = m_cur * sl2;
-            const float a_eff = (l_run == 0.f) ? 0.f : ex2_approx(ms_prev - ms);
-            s_alpha[(j & 3) * 128 + r] = a_eff;
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(bar(bMX + par * 4 + quarter));
-                mbar_arrive(bar(bAR + (j & 3)));
-            }
-            if (p.debug != nullptr && blockIdx.x == 0 && j == 0) p.debug[16384 + r] = m_new;
-            const float max_scaled = empty ? 0.f : fmaf(m_new, sl2, kPScaleLog2);
-            float negc[8], sfv[8];
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                const bool gdead = (bm[g] == -INFINITY);
-                // sf = max(P~) / 6 = 2^(bm s - max_scaled - log2 6);  negc = -(bm s - log2 6)
-                negc[g] = gdead ? 0.f : -fmaf(bm[g], sl2, -kLog2Of6);
-                sfv[g] = gdead ? 0.f : ex2_approx(fmaf(bm[g], sl2, -max_scaled) - kLog2Of6);
-            }
-            PT(2)
-            // P buffer `par` was last read by the PV MMA of block j - 2
-            if (j >= 2 && !warp_wait(bar(bPV + (j - 2) % S), ((j - 2) / S) & 1, abort_flag, p.status, kWaitPEmpty)) { alive = false; break; }
-            PT(1)
-            uint32_t codes[4];
+            uint32_t codes[16];
             uint32_t sfb[2] = {0, 0};
             float rowsum = 0.f;
 #pragma unroll
@@ -423,18 +391,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 float se0, se1;
                 unpack2f(add2(acc0, acc1), se0, se1);
                 rowsum = fmaf(sfv[g], se0 + se1, rowsum);
-                codes[2 * (g & 1)] = cvt_e2m1x8(e[0], e[1], e[2], e[3], e[4], e[5], e[6], e[7]);
-                codes[2 * (g & 1) + 1] = cvt_e2m1x8(e[8], e[9], e[10], e[11], e[12], e[13], e[14], e[15]);
+                codes[2 * g] = cvt_e2m1x8(e[0], e[1], e[2], e[3], e[4], e[5], e[6], e[7]);
+                codes[2 * g + 1] = cvt_e2m1x8(e[8], e[9], e[10], e[11], e[12], e[13], e[14], e[15]);
                 sfb[g >> 2] |= (cvt_e4m3x2(sfv[g], 0.f) & 0xffu) << (8 * (g & 3));
-                // P codes: every two microblocks fill one 16-byte chunk of the 64-byte-swizzled K-major row
-                if (g & 1)
-                    *reinterpret_cast<uint4*>(prow + (((g >> 1) ^ sw) << 4)) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
             }
+            // row sum relative to the running maximum of this block: rescale what this warpgroup has so far
+            const float a_eff = (l_run == 0.f) ? 0.f : ex2_approx(ms_prev - ms);
             l_run = fmaf(l_run, a_eff, rowsum);
             ms_prev = ms;
             if (p.debug != nullptr && blockIdx.x == 0 && j == 0) p.debug[16384 + 128 + r] = rowsum;
             PT(0)
-            // scales of P: one word per 64-key atom
+            // P buffer `par` was last read by the PV MMA of block j - 2
+            if (j >= 2 && !warp_wait(bar(bPE + par), ((j >> 1) - 1) & 1, abort_flag, p.status, kWaitPEmpty)) { alive = false; break; }
+            // P codes: four 16-byte chunks of the 64-byte-swizzled K-major row; scales: one word per 64-key atom
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                *reinterpret_cast<uint4*>(prow + ((c ^ sw) << 4)) =
+                    make_uint4(codes[4 * c], codes[4 * c + 1], codes[4 * c + 2], codes[4 * c + 3]);
             sfp_row[0] = sfb[0];
             sfp_row[128] = sfb[1];
             fence_proxy_async_smem();
@@ -452,87 +425,140 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         __syncwarp();
     } else {
-        reg_dealloc<80>();
-        // ------------------------------------------------------------------ correction + epilogue (4 warps)
-        // Thread = row r.  Before the PV MMA of block j, O is multiplied by the block's rescale factor (published
-        // by the exp warps; only when some row of the warp moved its maximum).  At the end O / l goes to global
-        // memory.
+        reg_dealloc<96>();
+        // ------------------------------------------------------------------ stats + correction + epilogue (4 warps)
+        // Thread = row r.  For every block, ahead of the exp warps: microblock maxima of the whole row, running
+        // maximum, rescale factor and the per-microblock constants, published through shared memory.  Then O is
+        // multiplied by the rescale factor before the block's PV MMA (only when some row of the warp moved its
+        // maximum).  At the end O / l goes to global memory.
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;
         const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
         const int grow = mt * kBlock + r;
+        float m_run = -INFINITY;
         bool alive = true;
         PT_DECL
-        for (int j = 0; j < nb; ++j) {
-            if (!warp_wait(bar(bAR + (j & 3)), (j >> 2) & 1, abort_flag, p.status, kWaitAlpha)) { alive = false; break; }
-            const float alpha = s_alpha[(j & 3) * 128 + r];
+        // statistics of block j: constants into shared memory, rescale factor returned
+        auto do_stats = [&](int j, float& alpha_out) -> bool {
+            const int n = nb - 1 - j, bb = j & 1;
+            if (!warp_wait(bar(bSF + bb), (j >> 1) & 1, abort_flag, p.status, kWaitSFull)) return false;
             PT(0)
-            if (j >= 2) {
-                // the accumulator of this parity was last written by the PV MMA of block j - 2
-                if (!warp_wait(bar(bPV + (j - 2) % S), ((j - 2) / S) & 1, abort_flag, p.status, kWaitOReady)) { alive = false; break; }
+            tc_fence_after();
+            const bool need_mask = ((n + 1) * kBlock > p.Nk) || (CAUSAL && (n * kBlock + kBlock - 1 > mt * kBlock + shift));
+            int lim = p.Nk - 1;
+            if (CAUSAL) lim = min(lim, grow + shift);
+            auto mask32 = [&](float* t, int c4) {
+                const int key0 = n * kBlock + c4 * 32;
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (key0 + i > lim) t[i] = -INFINITY;
+            };
+            const uint32_t sa = tmem + lane_addr + (bb ? C::cS1 : C::cS0);
+            float bm[8];
+            float t0[32], t1[32];
+            // two loads in flight at a time
+            tmem_ld32(sa, t0);
+            tmem_ld32(sa + 32, t1);
+            tc_wait_ld();
+            if (need_mask) { mask32(t0, 0); mask32(t1, 1); }
+            microblock_max2(t0, bm[0], bm[1]);
+            microblock_max2(t1, bm[2], bm[3]);
+            tmem_ld32(sa + 64, t0);
+            tmem_ld32(sa + 96, t1);
+            tc_wait_ld();
+            if (need_mask) { mask32(t0, 2); mask32(t1, 3); }
+            microblock_max2(t0, bm[4], bm[5]);
+            microblock_max2(t1, bm[6], bm[7]);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(bSE + bb));
+            PT(1)
+            const float m_new = fmaxf(fmax3(m_run, bm[0], bm[1]), fmaxf(fmax3(bm[2], bm[3], bm[4]), fmax3(bm[5], bm[6], bm[7])));
+            const bool empty = (m_new == -INFINITY);
+            const float m_cur = empty ? 0.f : m_new;
+            alpha_out = ex2_approx((m_run - m_cur) * sl2);        // m_run = -inf  ->  0
+            const float max_scaled = empty ? 0.f : fmaf(m_new, sl2, kPScaleLog2);
+            float* cst = s_cst + bb * (17 * 128);
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                const bool gdead = (bm[g] == -INFINITY);
+                // sf = max(P~) / 6 = 2^(bm s - max_scaled - log2 6);  negc = -(bm s - log2 6)
+                cst[g * 128 + r] = gdead ? 0.f : -fmaf(bm[g], sl2, -kLog2Of6);
+                cst[(8 + g) * 128 + r] = gdead ? 0.f : ex2_approx(fmaf(bm[g], sl2, -max_scaled) - kLog2Of6);
+            }
+            cst[16 * 128 + r] = m_cur * sl2;      // scaled running maximum the exp2 values of this block refer to
+            m_run = m_new;
+            if (p.debug != nullptr && blockIdx.x == 0 && j == 0) p.debug[16384 + r] = m_new;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(bST + bb));
+            PT(2)
+            return true;
+        };
+        float alpha = 1.f;
+        if (nb > 0) alive = do_stats(0, alpha);
+        for (int j = 0; alive && j < nb; ++j) {
+            // statistics run one block ahead of the rescaling, so the exp warps never wait for a PV MMA
+            float alpha_next = 1.f;
+            if (j + 1 < nb && !do_stats(j + 1, alpha_next)) { alive = false; break; }
+            if (j > 0) {
+                if (!warp_wait(bar(bOR), (j - 1) & 1, abort_flag, p.status, kWaitOReady)) { alive = false; break; }
                 PT(3)
                 if (__any_sync(0xffffffffu, alpha != 1.0f)) {
                     tc_fence_after();
                     const uint64_t a2 = pack2f(alpha, alpha);
 #pragma unroll
-                    for (int cc = 0; cc < D / 32; ++cc) {
-                        float o[32];
-                        const uint32_t o_addr = tmem + lane_addr + ((j & 1) ? C::cO1 : C::cO0) + cc * 32;
-                        tmem_ld32(o_addr, o);
+                    for (int cc = 0; cc < D / 64; ++cc) {
+                        float o0[32], o1[32];
+                        const uint32_t o_addr = tmem + lane_addr + C::cO + cc * 64;
+                        tmem_ld32(o_addr, o0);
+                        tmem_ld32(o_addr + 32, o1);
                         tc_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) unpack2f(mul2(pack2f(o[2 * i], o[2 * i + 1]), a2), o[2 * i], o[2 * i + 1]);
-                        tmem_st32(o_addr, o);
+                        for (int i = 0; i < 16; ++i) {
+                            unpack2f(mul2(pack2f(o0[2 * i], o0[2 * i + 1]), a2), o0[2 * i], o0[2 * i + 1]);
+                            unpack2f(mul2(pack2f(o1[2 * i], o1[2 * i + 1]), a2), o1[2 * i], o1[2 * i + 1]);
+                        }
+                        tmem_st32(o_addr, o0);
+                        tmem_st32(o_addr + 32, o1);
                     }
                     tc_wait_st();
                 }
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(bOS + (j & 1)));
+            if (lane == 0) mbar_arrive(bar(bOS));
+            alpha = alpha_next;
             PT(4)
         }
         PT_DUMP(warp)
         if (alive && !dead_launch) {
-            // Each softmax warpgroup's row sum and O accumulator refer to the maximum of its own last block; the
-            // warpgroup of the last block holds the final maximum.  out = (w0 O0 + w1 O1) / (w0 l0 + w1 l1).
-            float l_tot = 0.f, w0 = 0.f, w1 = 0.f;
+            float l_tot = 0.f;
             if (nb > 0) {
                 alive = warp_wait(bar(bLR), 0, abort_flag, p.status, kWaitAlpha);
-                if (alive) alive = warp_wait(bar(bPV + (nb - 1) % S), ((nb - 1) / S) & 1, abort_flag, p.status, kWaitOReady);
-                if (alive && nb > 1) alive = warp_wait(bar(bPV + (nb - 2) % S), ((nb - 2) / S) & 1, abort_flag, p.status, kWaitOReady);
+                if (alive) alive = warp_wait(bar(bOR), (nb - 1) & 1, abort_flag, p.status, kWaitOReady);
                 if (alive) {
                     tc_fence_after();
-                    const float ms_final = s_l[((nb - 1) & 1) * 256 + 128 + r];
-                    const float l0 = s_l[r], l1 = s_l[256 + r];
-                    if (l0 != 0.f) w0 = ex2_approx(s_l[128 + r] - ms_final);
-                    if (l1 != 0.f) w1 = ex2_approx(s_l[256 + 128 + r] - ms_final);
-                    l_tot = l0 * w0 + l1 * w1;
+                    // each exp warpgroup's sum refers to the maximum of its own last block: bring both to the final one
+                    const float ms_final = (m_run == -INFINITY ? 0.f : m_run) * sl2;
+#pragma unroll
+                    for (int w2 = 0; w2 < 2; ++w2) {
+                        const float lw = s_l[w2 * 256 + r], lm = s_l[w2 * 256 + 128 + r];
+                        if (lw != 0.f) l_tot += lw * ex2_approx(lm - ms_final);
+                    }
                 }
             }
             if (alive) {
                 const float inv_l = (l_tot == 0.f || l_tot != l_tot) ? 0.f : __frcp_rn(l_tot);
-                w0 *= inv_l;
-                w1 *= inv_l;
-                const bool use1 = __any_sync(0xffffffffu, w1 != 0.f) && nb > 1;   // accumulator 1 exists only with >= 2 blocks
                 OutT* orow = static_cast<OutT*>(p.out) + b * p.os0 + hq * p.os1 + (int64_t)grow * p.os2;
 #pragma unroll
                 for (int cc = 0; cc < D / 32; ++cc) {
                     float o[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = 0.f;
                     if (nb > 0) {
-                        tmem_ld32(tmem + lane_addr + C::cO0 + cc * 32, o);
+                        tmem_ld32(tmem + lane_addr + C::cO + cc * 32, o);
                         tc_wait_ld();
+                    } else {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] *= w0;
-                        if (use1) {
-                            float o1[32];
-                            tmem_ld32(tmem + lane_addr + C::cO1 + cc * 32, o1);
-                            tc_wait_ld();
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) o[i] = fmaf(o1[i], w1, o[i]);
-                        }
+                        for (int i = 0; i < 32; ++i) o[i] = 0.f;
                     }
                     if (p.debug != nullptr && blockIdx.x == 0) {
 #pragma unroll
@@ -543,10 +569,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             uint4 w;
-                            w.x = pack2<OutT>(o[8 * i], o[8 * i + 1]);
-                            w.y = pack2<OutT>(o[8 * i + 2], o[8 * i + 3]);
-                            w.z = pack2<OutT>(o[8 * i + 4], o[8 * i + 5]);
-                            w.w = pack2<OutT>(o[8 * i + 6], o[8 * i + 7]);
+                            w.x = pack2<OutT>(o[8 * i] * inv_l, o[8 * i + 1] * inv_l);
+                            w.y = pack2<OutT>(o[8 * i + 2] * inv_l, o[8 * i + 3] * inv_l);
+                            w.z = pack2<OutT>(o[8 * i + 4] * inv_l, o[8 * i + 5] * inv_l);
+                            w.w = pack2<OutT>(o[8 * i + 6] * inv_l, o[8 * i + 7] * inv_l);
                             *reinterpret_cast<uint4*>(orow + cc * 32 + i * 8) = w;
                         }
                     }
