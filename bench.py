@@ -292,6 +292,13 @@ def main():
     ms_per_step = total_ms / args.steps
     att_tops = flops / (att_ms * 1e-3) / 1e12
     fp4_peak = 4.0 * peaks["bf16_sustained"]          # dense FP4 is 4x dense bf16 on this part
+    # DRAM traffic of one attention launch: ncu measured 163.1 MB (dram__bytes_read.sum + dram__bytes_write.sum) on
+    # the ncu_small case (16 heads x 16384 tokens, D=128; profiles/attn_fwd_kernel__ncu_small.md); the kernel reads
+    # each head's operands once from DRAM and writes its output once, so traffic scales with B*H*N*D.
+    traffic, traffic_src = None, None
+    if D == 128 and not w["causal"]:
+        traffic = 163.1e6 * (B * Hq * Nq) / (16 * 16384.0)
+        traffic_src = "scaled from one ncu capture of the ncu_small case in proportion to B*H*N"
     line = dict(
         metric="attention TOPS (4*B*H*Nq*Nk*D/t) of the smooth+NVFP4-quantize+attend path", value=world * flops / (ms_per_step * 1e-3) / 1e12,
         unit="TOPS", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=ms_per_step, higher_is_better=True,
@@ -303,7 +310,7 @@ def main():
                                                                  frac_of_hbm_peak=prepass_bytes_of(w) / (pre_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                                                                  algorithmic_bytes=prepass_bytes_of(w)),
         roofline=dict(bound="tensor", kernel="attn_fwd_kernel", achieved=att_tops, peak=fp4_peak, unit="TFLOP/s", frac=att_tops / fp4_peak,
-                      traffic=None, peak_source=f"4 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']})",
+                      traffic=traffic, traffic_source=traffic_src, peak_source=f"4 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']})",
                       frac_of_nominal_fp4=att_tops / NOMINAL_FP4_TFLOPS),
         clocks=clocks, e2e=e2e, gpu_launches=6 * args.steps,
     )
