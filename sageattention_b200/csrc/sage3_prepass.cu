@@ -32,13 +32,19 @@ template <> struct Num<__half> {
     }
 };
 
+// 16 elements stay packed in two 128-bit registers until they are needed (keeps the register count, and with it
+// the number of resident CTAs, where an HBM-bound kernel needs it)
 template <typename T>
-__device__ __forceinline__ void load16(const T* p, bool valid, float* f) {   // 16 elements -> fp32
-    uint4 a = make_uint4(0, 0, 0, 0), b = a;
+__device__ __forceinline__ void load16_packed(const T* p, bool valid, uint4& a, uint4& b) {
+    a = make_uint4(0, 0, 0, 0);
+    b = a;
     if (valid) {
         a = __ldg(reinterpret_cast<const uint4*>(p));
         b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
     }
+}
+template <typename T>
+__device__ __forceinline__ void unpack16(const uint4& a, const uint4& b, float* f) {   // 16 elements -> fp32
     const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -165,23 +171,27 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(
     float* s_red = reinterpret_cast<float*>(s_sf + (D / 64) * 512);            // [8 warps][D] (block mean)
     T* s_k = reinterpret_cast<T*>(reinterpret_cast<uint8_t*>(s_red) + 8 * D * 4);   // [128][PITCH]  (K mode)
     T* s_a = s_k + kBlock * PITCH;                                                  // [MCH][PITCH] (K mode)
+    constexpr int DPITCH = kBlock + 8;    // staging pitch of a 128-key delta_s row
+    T* s_d = s_a + MCH * PITCH;                                                     // [MCH][DPITCH] (K mode) delta_s staging
 
-    float v[ITEMS][16];
+    uint4 raw[ITEMS][2];
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
         const int r = row0 + rl + RPP * i;
-        load16<T>(base + (int64_t)r * sn + c * 16, r < N, v[i]);
+        load16_packed<T>(base + (int64_t)r * sn + c * 16, r < N, raw[i][0], raw[i][1]);
     }
 
     if (MODE == kModeQBlockMean) {
         // column sums over the tile's 128 rows (rows beyond N are zero and count, as padding precedes the mean)
         float acc[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            float s = 0.f;
+        for (int j = 0; j < 16; ++j) acc[j] = 0.f;
 #pragma unroll
-            for (int i = 0; i < ITEMS; ++i) s += v[i][j];
-            acc[j] = s;
+        for (int i = 0; i < ITEMS; ++i) {
+            float f[16];
+            unpack16<T>(raw[i][0], raw[i][1], f);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[j] += f[j];
         }
         // lanes sharing c inside a warp: lane = c + CH * k
 #pragma unroll
@@ -217,9 +227,10 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(
         const int rt = rl + RPP * i;          // row inside the tile
         const int r = row0 + rt;
         float y[16];
+        unpack16<T>(raw[i][0], raw[i][1], y);
         const bool zero_row = (MODE == kModeK) && (r >= N);   // K is padded after smoothing: pad rows are 0
 #pragma unroll
-        for (int j = 0; j < 16; ++j) y[j] = zero_row ? 0.f : Num<T>::to_f(Num<T>::from_f(v[i][j] - mu[j]));
+        for (int j = 0; j < 16; ++j) y[j] = zero_row ? 0.f : Num<T>::to_f(Num<T>::from_f(y[j] - mu[j]));
         uint32_t lo, hi, sfb;
         quant16(y, lo, hi, sfb);
         *reinterpret_cast<uint2*>(codes + ((int64_t)bh * Np + r) * (D / 2) + c * 8) = make_uint2(lo, hi);
@@ -288,21 +299,26 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(
                         mma16816<T>(acc[mt][1], af, bf[2], bf[3]);
                     }
                 }
+                // stage the 64 x 128 result in shared memory, then write whole 256-byte rows
 #pragma unroll
                 for (int mt = 0; mt < MCH / 16; ++mt)
 #pragma unroll
                     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                         for (int half = 0; half < 2; ++half) {
-                            const int qb = m0 + mt * 16 + (lane >> 2) + 8 * half;
-                            if (qb < nqm) {
-                                const int n = row0 + warp * 16 + nt * 8 + 2 * (lane & 3);
-                                typename Num<T>::T2 p;
-                                p.x = Num<T>::from_f(acc[mt][nt][2 * half]);
-                                p.y = Num<T>::from_f(acc[mt][nt][2 * half + 1]);
-                                *reinterpret_cast<typename Num<T>::T2*>(dh + (int64_t)qb * Np + n) = p;
-                            }
+                            typename Num<T>::T2 p;
+                            p.x = Num<T>::from_f(acc[mt][nt][2 * half]);
+                            p.y = Num<T>::from_f(acc[mt][nt][2 * half + 1]);
+                            *reinterpret_cast<typename Num<T>::T2*>(s_d + (mt * 16 + (lane >> 2) + 8 * half) * DPITCH + warp * 16 +
+                                                                    nt * 8 + 2 * (lane & 3)) = p;
                         }
+                __syncthreads();
+                for (int idx = t; idx < MCH * 16; idx += 256) {
+                    const int rr = idx >> 4, c16 = idx & 15;
+                    if (m0 + rr < nqm)
+                        *reinterpret_cast<uint4*>(dh + (int64_t)(m0 + rr) * Np + row0 + c16 * 8) =
+                            *reinterpret_cast<const uint4*>(s_d + rr * DPITCH + c16 * 8);
+                }
             }
         }
     }
@@ -383,7 +399,7 @@ static cudaError_t launch_prepass_t(const PrepassArgs& a, cudaStream_t st) {
     colmean_finalize_kernel<T, D><<<BHkv, D, 0, st>>>(a.kpart, a.kchunks_k, 1.0f / (float)a.Nk, km);
 
     const size_t smem_q = D * 4 + (D / 64) * 512 + 8 * D * 4;
-    const size_t smem_k = smem_q + (size_t)(kBlock + 64) * (D + 8) * sizeof(T);
+    const size_t smem_k = smem_q + (size_t)(kBlock + 64) * (D + 8) * sizeof(T) + (size_t)64 * (kBlock + 8) * sizeof(T);
     if (a.per_block_mean) {
         quant_rows_kernel<T, D, kModeQBlockMean><<<dim3(a.Nq_p / kBlock, BHq), 256, smem_q, st>>>(
             q, a.qs[0], a.qs[1], a.qs[2], a.Hq, a.Nq, a.Nq_p, nullptr, qm, a.q_codes, a.q_sf, nullptr, nullptr, 0, 0);
