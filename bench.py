@@ -158,6 +158,43 @@ def run_reference(args, w):
     print(json.dumps(line))
 
 
+def run_ulysses(args, w, q, k, v, flops, rank, world, local, dev):
+    """Strong-scaling arm: one step = all-to-all, pre-pass, attention, all-to-all on every rank."""
+    import torch
+    import torch.distributed as dist
+    from sageattention_b200.ulysses import ulysses_attention
+    stream = torch.cuda.current_stream()
+    for _ in range(max(args.warmup, 3)):
+        ulysses_attention(q, k, v, tensor_layout=w["layout"])
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    dist.barrier()
+    torch.cuda.synchronize()
+    a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(args.steps):
+        ulysses_attention(q, k, v, tensor_layout=w["layout"])
+    b_.record(stream)
+    torch.cuda.synchronize()
+    dist.barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([a.elapsed_time(b_) / args.steps], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item()
+    if rank == 0:
+        per_rank_bytes = 4 * (world - 1) / world * q.numel() * 2      # q, k, v out and o back, 16-bit
+        print(json.dumps(dict(
+            metric="attention TOPS (4*B*H*Nq*Nk*D/t) of the smooth+NVFP4-quantize+attend path", value=flops / (ms * 1e-3) / 1e12, unit="TOPS",
+            n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=ms, higher_is_better=True, scaling="strong",
+            vs_baseline=None, dtype="fp4 (e2m1 x ue4m3), fp32 accumulate", data="synthetic",
+            config=dict(workload=args.workload, sharding="ulysses sequence parallel: NCCL all-to-all before and after attention",
+                        tokens_per_rank=q.shape[2] if w["layout"] == "HND" else q.shape[1], heads_per_rank=w["Hq"] // world,
+                        all_to_all_bytes_per_rank_per_step=per_rank_bytes, l2="inputs larger than L2"),
+            clocks=clocks, gpu_launches=6 * args.steps)))
+    dist.destroy_process_group()
+
+
 # --------------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -168,6 +205,8 @@ def main():
     ap.add_argument("--impl", default="sage3_b200", choices=["sage3_b200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ulysses", action="store_true",
+                    help="strong scaling: the workload's tokens are sharded over the ranks (all-to-all before and after attention)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
@@ -192,6 +231,10 @@ def main():
     # seeded synthetic input, generated on the device in chunks (the full tensors are several GB)
     g = torch.Generator(device=dev).manual_seed(2000 + rank)
     B, Hq, Hkv, Nq, Nk, D = (w[k_] for k_ in ("B", "Hq", "Hkv", "Nq", "Nk", "D"))
+    if args.ulysses:
+        if Nq % world or Nk % world or Hq % world or Hkv % world or w["causal"]:
+            raise SystemExit("--ulysses needs token and head counts divisible by the number of GPUs and a non-causal workload")
+        Nq, Nk = Nq // world, Nk // world       # this rank's token shard
     shp_q = (B, Hq, Nq, D) if w["layout"] == "HND" else (B, Nq, Hq, D)
     shp_k = (B, Hkv, Nk, D) if w["layout"] == "HND" else (B, Nk, Hkv, D)
     q = torch.empty(shp_q, dtype=torch.bfloat16, device=dev).normal_(generator=g)
@@ -206,9 +249,12 @@ def main():
         k[..., idx] *= 2
     # (RoPE of the Llama-shaped workload changes values, not shapes or timing; the parity tests cover it.)
 
-    prob = Sage3Problem(q, k, v, tensor_layout=w["layout"], is_causal=w["causal"])
     flops = flops_of(w)
     stream = torch.cuda.current_stream()
+    if args.ulysses and world > 1:
+        run_ulysses(args, w, q, k, v, flops, rank, world, local, dev)
+        return
+    prob = Sage3Problem(q, k, v, tensor_layout=w["layout"], is_causal=w["causal"])
 
     def step(ev=None):
         if ev is not None:

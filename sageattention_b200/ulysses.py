@@ -1,0 +1,104 @@
+"""Multi-GPU partitioning of the attention path on one NVSwitch box (one process per GPU, NCCL).
+
+Two schemes, as the reference's parallel example uses them through xfuser
+(reference: example/parallel_sageattn_cogvideo.py:8-14, 89-95; no collective exists in the reference itself):
+
+* independent units: (batch, kv-head) pairs are split across ranks, every rank runs the whole path on its
+  shard, nothing is exchanged (`shard_units`);
+* Ulysses sequence parallelism for long sequences: every rank holds a token shard of all heads; one
+  all-to-all turns that into all tokens of H/P heads, attention runs locally (smoothing means and NVFP4
+  quantization need the whole sequence of a head, so they run after the exchange), a second all-to-all
+  returns the output to token shards (`ulysses_attention`).
+
+The exchanged tensors land in this GPU's own memory before any kernel reads them.
+"""
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+
+
+def shard_units(B: int, Hkv: int, rank: int, world: int) -> list[tuple[int, int]]:
+    """(batch, kv-head) units of `rank`: contiguous, sizes differing by at most one.  All query heads of a
+    kv head stay with it, so K, V and the K mean are loaded once."""
+    units = [(b, h) for b in range(B) for h in range(Hkv)]
+    base, extra = divmod(len(units), world)
+    start = rank * base + min(rank, extra)
+    return units[start: start + base + (1 if rank < extra else 0)]
+
+
+# ------------------------------------------------------------------------------------------------------
+# layout helpers (pure tensor reshuffles; tested on CPU by simulating the exchange)
+# ------------------------------------------------------------------------------------------------------
+def _to_hnd(x: torch.Tensor, tensor_layout: str) -> torch.Tensor:
+    if tensor_layout == "HND":
+        return x
+    if tensor_layout == "NHD":
+        return x.transpose(1, 2)
+    raise ValueError(f"tensor_layout must be 'HND' or 'NHD', got {tensor_layout!r}")
+
+
+def pack_heads_for_exchange(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, world: int) -> torch.Tensor:
+    """q [B,Hq,n,D], k/v [B,Hkv,n,D] (token shard, all heads) -> send buffer [P, B, (Hq+2Hkv)/P, n, D]:
+    slice p holds the heads destined to rank p (its query heads, then its k heads, then its v heads)."""
+    B, Hq, n, D = q.shape
+    Hkv = k.shape[1]
+    if Hq % world or Hkv % world:
+        raise ValueError(f"Ulysses needs the head counts ({Hq}, {Hkv}) to be multiples of the world size {world}")
+    parts = [q.reshape(B, world, Hq // world, n, D), k.reshape(B, world, Hkv // world, n, D),
+             v.reshape(B, world, Hkv // world, n, D)]
+    return torch.cat(parts, dim=2).permute(1, 0, 2, 3, 4).contiguous()
+
+
+def unpack_heads_after_exchange(recv: torch.Tensor, Hq_local: int, Hkv_local: int):
+    """recv [P (source rank = token shard), B, Hq_l+2Hkv_l, n, D] -> q [B,Hq_l,P*n,D], k, v [B,Hkv_l,P*n,D]."""
+    P, B, _, n, D = recv.shape
+    full = recv.permute(1, 2, 0, 3, 4).reshape(B, -1, P * n, D)
+    q, k, v = torch.split(full, [Hq_local, Hkv_local, Hkv_local], dim=1)
+    return q, k, v
+
+
+def pack_tokens_for_exchange(o: torch.Tensor, world: int) -> torch.Tensor:
+    """o [B,Hq_l,N,D] (all tokens, local heads) -> send buffer [P, B, Hq_l, N/P, D]: slice p = token shard p."""
+    B, H, N, D = o.shape
+    return o.reshape(B, H, world, N // world, D).permute(2, 0, 1, 3, 4).contiguous()
+
+
+def unpack_tokens_after_exchange(recv: torch.Tensor) -> torch.Tensor:
+    """recv [P (source rank = head group), B, Hq_l, n, D] -> o [B, P*Hq_l, n, D]."""
+    P, B, H, n, D = recv.shape
+    return recv.permute(1, 0, 2, 3, 4).reshape(B, P * H, n, D)
+
+
+# ------------------------------------------------------------------------------------------------------
+def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
+                      is_causal: bool = False, group: dist.ProcessGroup | None = None,
+                      attn_fn: Callable | None = None, **kwargs) -> torch.Tensor:
+    """Sequence-parallel attention.  Every rank passes its contiguous token shard
+    [rank * N/P, (rank + 1) * N/P) of all heads and gets the output for the same shard.
+
+    q: [B, Hq, N/P, D] ("HND") or [B, N/P, Hq, D] ("NHD"); k, v likewise with Hkv.  Hq and Hkv must be
+    multiples of the group size.  `attn_fn(q, k, v, tensor_layout="HND", is_causal=..., **kwargs)` defaults to
+    sageattn3; the result equals attn_fn on the gathered tensors, bit for bit, because every head is
+    computed by exactly one rank from exactly the same inputs.
+    """
+    if attn_fn is None:
+        from .api import sageattn3 as attn_fn
+    world = dist.get_world_size(group)
+    qh, kh, vh = (_to_hnd(t, tensor_layout) for t in (q, k, v))
+    if world == 1:
+        o = attn_fn(qh.contiguous(), kh.contiguous(), vh.contiguous(), tensor_layout="HND", is_causal=is_causal, **kwargs)
+    else:
+        Hq, Hkv = qh.shape[1], kh.shape[1]
+        send = pack_heads_for_exchange(qh, kh, vh, world)
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=group)
+        ql, kl, vl = unpack_heads_after_exchange(recv, Hq // world, Hkv // world)
+        ol = attn_fn(ql.contiguous(), kl.contiguous(), vl.contiguous(), tensor_layout="HND", is_causal=is_causal, **kwargs)
+        send_o = pack_tokens_for_exchange(ol, world)
+        recv_o = torch.empty_like(send_o)
+        dist.all_to_all_single(recv_o, send_o, group=group)
+        o = unpack_tokens_after_exchange(recv_o)
+    return o if tensor_layout == "HND" else o.transpose(1, 2)
