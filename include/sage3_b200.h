@@ -137,6 +137,28 @@ SAGE3_API int sage3_check_status(const void* ws, int32_t* word, void* stream);
  */
 SAGE3_API int sage3_attn_fwd_debug(const Sage3Desc* desc, void* ws, void* out, float* debug, void* stream);
 
+/*
+ * Mean of K over its Nk tokens, per (batch, kv-head) and channel -- the first stage of the pre-pass -- for
+ * callers that must not allocate device memory and cannot hand over a workspace: for instance a serving
+ * engine that gave all device memory to its own pool at start-up, or a latency-critical loop in which a
+ * cudaMalloc (and the device-wide synchronization it implies) is not acceptable.  It has no counterpart in
+ * the reference.
+ *
+ * km_out[b][h][d] (element type desc->dtype, B*Hkv*D elements, caller-allocated device memory) receives exactly
+ * the values sage3_prepass leaves in the `km` region of its workspace.  Only B, Hkv, Nk, D, dtype and k_stride
+ * of `desc` are read.  The partial sums go to a fixed array that lives inside the library image on every GPU
+ * that loads it (SAGE3_KMEAN_NOALLOC_MAX_FLOATS floats = 4 MiB, held until the process exits); the call
+ * returns SAGE3_E_TOO_LARGE when B*Hkv*ceil(Nk/512)*D exceeds that many floats.  The function calls no
+ * cudaMalloc / cudaFree and no allocating library routine.
+ *
+ * The first call on each device looks the array's device address up (that device must be current); make that
+ * first call before any stream capture begins.  All calls on a device share the one array, which keeps the
+ * previous call's contents (nothing in it needs clearing: each call overwrites what it reads): two calls
+ * whose kernels may overlap on the GPU -- different streams without an ordering between them -- race on it.
+ */
+#define SAGE3_KMEAN_NOALLOC_MAX_FLOATS (1u << 20)
+SAGE3_API int sage3_kmean_noalloc(const Sage3Desc* desc, const void* k, void* km_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -9,6 +9,9 @@
 //   quantization/fp4_quantization_4d.cu:185-225   SF = e4m3(amax / 6), code = e2m1(x * (1 / SF))
 //   quantization/fp4_quantization_4d.cu:300-349   V: microblocks are 16 consecutive tokens of one channel
 // Divisions and reciprocals are IEEE (div.rn / rcp.rn) so the result can be checked bit for bit.
+#include <mutex>
+
+#include "../../include/sage3_b200.h"
 #include "sage3_common.cuh"
 #include "sage3_kernels.h"
 
@@ -434,3 +437,75 @@ cudaError_t launch_prepass(const PrepassArgs& a, cudaStream_t st) {
 }
 
 }  // namespace sage3
+
+// ------------------------------------------------------------------------------------------------
+// K mean without any allocation by anybody: the partial column sums live in a static device array
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+// Scratch for sage3_kmean_noalloc: partial column sums [B*Hkv][chunks][D] in fp32.  Every GPU that loads this
+// library holds these 4 MiB until the process exits.  Inside host code this name is only a stand-in for the
+// device array; the device address is obtained once per device with cudaGetSymbolAddress (below).
+static __device__ __align__(256) float g_kmean_scratch[SAGE3_KMEAN_NOALLOC_MAX_FLOATS];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+float* g_scratch_addr[kMaxDevices] = {};   // device address of g_kmean_scratch on each device, once resolved
+
+// Device address of the scratch array on the current device; resolved on the first call per device.
+int scratch_for_current_device(float** out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return SAGE3_E_CUDA;
+    if (dev < 0 || dev >= kMaxDevices) return SAGE3_E_TOO_LARGE;
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (g_scratch_addr[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_kmean_scratch) != cudaSuccess || p == nullptr) return SAGE3_E_CUDA;
+        g_scratch_addr[dev] = static_cast<float*>(p);
+    }
+    *out = g_scratch_addr[dev];
+    return SAGE3_OK;
+}
+
+template <typename T, int D>
+cudaError_t launch_kmean_t(const Sage3Desc* d, const void* k, void* km, float* scratch, int chunks, cudaStream_t st) {
+    const int BH = d->B * d->Hkv;
+    sage3::colsum_partial_kernel<T, D><<<dim3(chunks, BH), 256, 0, st>>>(
+        static_cast<const T*>(k), d->k_stride[0], d->k_stride[1], d->k_stride[2], d->Hkv, d->Nk, scratch, chunks);
+    sage3::colmean_finalize_kernel<T, D><<<BH, D, 0, st>>>(scratch, chunks, 1.0f / (float)d->Nk, static_cast<T*>(km));
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" SAGE3_API int sage3_kmean_noalloc(const Sage3Desc* desc, const void* k, void* km_out, void* stream) {
+    if (!desc || !k || !km_out) return SAGE3_E_NULL;
+    if (desc->B <= 0 || desc->Hkv <= 0 || desc->Nk <= 0 || (desc->D != 64 && desc->D != 128)) return SAGE3_E_SHAPE;
+    if (desc->dtype != SAGE3_FP16 && desc->dtype != SAGE3_BF16) return SAGE3_E_DTYPE;
+    for (int i = 0; i < 3; ++i)
+        if (desc->k_stride[i] < 0 || (desc->k_stride[i] % 8) != 0) return SAGE3_E_STRIDE;
+    if ((reinterpret_cast<uintptr_t>(k) % 16) != 0 || (reinterpret_cast<uintptr_t>(km_out) % 2) != 0) return SAGE3_E_ALIGN;
+    const int64_t chunks = ((int64_t)desc->Nk + sage3::kRowsPerChunk - 1) / sage3::kRowsPerChunk;
+    const int64_t need = (int64_t)desc->B * desc->Hkv * chunks * desc->D;
+    if (need > (int64_t)SAGE3_KMEAN_NOALLOC_MAX_FLOATS || chunks > 65535) return SAGE3_E_TOO_LARGE;
+    int dev = 0, major = 0, minor = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev) != cudaSuccess)
+        return SAGE3_E_CUDA;
+    if (major != 10 || minor != 0) return SAGE3_E_ARCH;
+    float* scratch = nullptr;
+    const int rc = scratch_for_current_device(&scratch);
+    if (rc != SAGE3_OK) return rc;
+    // Nothing in the scratch has to start at zero: every partial sum the finalize step reads is written by the
+    // first kernel of this very call.
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    if (desc->dtype == SAGE3_BF16)
+        e = desc->D == 128 ? launch_kmean_t<__nv_bfloat16, 128>(desc, k, km_out, scratch, (int)chunks, st)
+                           : launch_kmean_t<__nv_bfloat16, 64>(desc, k, km_out, scratch, (int)chunks, st);
+    else
+        e = desc->D == 128 ? launch_kmean_t<__half, 128>(desc, k, km_out, scratch, (int)chunks, st)
+                           : launch_kmean_t<__half, 64>(desc, k, km_out, scratch, (int)chunks, st);
+    return e == cudaSuccess ? SAGE3_OK : SAGE3_E_CUDA;
+}
