@@ -86,7 +86,7 @@ struct Cfg {
     static constexpr int oCst = oOnes + 4096;                 // float [2][17][128]  per block: 8 offsets, 8 scales, scaled max per row
     static constexpr int oL = oCst + 2 * 17 * 128 * 4;        // float [2][2][128]   per exp warpgroup: row sum, scaled max it refers to
     static constexpr int oBar = oL + 4 * 128 * 4;
-    static constexpr int kNumBars = 1 + 4 * kStages + 2 + 2 + 2 + 2 + 1 + 1 + 2 + 1;
+    static constexpr int kNumBars = 1 + 4 * kStages + 2 + 2 + 1 + 2 + 1;
     static constexpr int oMisc = oBar + kNumBars * 8;
     static constexpr int kSmemBytes = oMisc + 64 + 1024;      // + slack for the manual 1024-byte alignment
     // tensor-memory columns
@@ -140,8 +140,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
     // barriers
     auto bar = [&](int i) { return sbase + C::oBar + 8u * i; };
-    const int bQ = 0, bKF = 1, bKE = bKF + S, bVF = bKE + S, bVE = bVF + S, bSF = bVE + S, bSE = bSF + 2,
-              bPF = bSE + 2, bPE = bPF + 2, bOR = bPE + 2, bOS = bOR + 1, bST = bOS + 1, bLR = bST + 2;
+    const int bQ = 0, bKF = 1, bQK = bKF + S, bVF = bQK + S, bPV = bVF + S, bSE = bPV + S, bPF = bSE + 2,
+              bOS = bPF + 2, bST = bOS + 1, bLR = bST + 2;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + C::oMisc);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + C::oMisc + 8);
 
@@ -165,18 +165,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mbar_init(bar(bQ), 1);
         for (int i = 0; i < S; ++i) {
             mbar_init(bar(bKF + i), 1);
-            mbar_init(bar(bKE + i), 1);
+            mbar_init(bar(bQK + i), 1);    // Q K^T (+ delta_s) of the block in stage i is complete: its S buffer is full, the K stage is free
             mbar_init(bar(bVF + i), 1);
-            mbar_init(bar(bVE + i), 1);
+            mbar_init(bar(bPV + i), 1);    // P V of the block in stage i is complete: O is up to date, V stage and P buffer are free
         }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(bar(bSF + i), 1);    // S buffer i holds Q K^T (+ delta_s)          (MMA commit)
             mbar_init(bar(bSE + i), 8);    // the exp warpgroup of the block (4 warps) and the stats warps (4) have read S buffer i
             mbar_init(bar(bST + i), 4);    // constants of the block in S buffer i are in shared memory  (stats warps)
             mbar_init(bar(bPF + i), 4);    // P buffer i (+ its scales) is written
-            mbar_init(bar(bPE + i), 1);    // the PV MMA that read P buffer i is complete  (MMA commit)
         }
-        mbar_init(bar(bOR), 1);            // PV of a block is complete: O is up to date  (MMA commit)
         mbar_init(bar(bOS), 4);            // O has been rescaled for the next PV          (stats warps)
         mbar_init(bar(bLR), 8);            // final row sums of both exp warpgroups are in shared memory
         mbar_fence_init();
@@ -225,13 +222,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const uint16_t* dptr = p.delta + ((size_t)bhq * p.nqm + drow) * ((size_t)p.nkb * kBlock);
             for (int j = 0; j < nb; ++j) {
                 const int n = nb - 1 - j, st = j % S;
-                if (j >= S && !mbar_wait<true>(bar(bKE + st), ((j / S) - 1) & 1, abort_flag, p.status, kWaitKEmpty)) break;
+                if (j >= S && !mbar_wait<true>(bar(bQK + st), ((j / S) - 1) & 1, abort_flag, p.status, kWaitKEmpty)) break;
                 mbar_expect_tx(bar(bKF + st), C::kKBytes + C::kSfQkBytes + C::kDeltaBytes);
                 tma_load_3d(sbase + C::oK + st * 8192, &tm_k, bar(bKF + st), 0, n * kBlock, bhkv);
                 bulk_load(sbase + C::oSfK + st * 1024, p.k_sf + ((size_t)bhkv * p.nkb + n) * C::kSfQkBytes,
                           C::kSfQkBytes, bar(bKF + st));
                 bulk_load(sbase + C::oDelta + st * C::kDeltaPitch, dptr + (size_t)n * kBlock, C::kDeltaBytes, bar(bKF + st));
-                if (j >= S && !mbar_wait<true>(bar(bVE + st), ((j / S) - 1) & 1, abort_flag, p.status, kWaitVEmpty)) break;
+                if (j >= S && !mbar_wait<true>(bar(bPV + st), ((j / S) - 1) & 1, abort_flag, p.status, kWaitVEmpty)) break;
                 mbar_expect_tx(bar(bVF + st), C::kVBytes + C::kSfVBytes);
                 tma_load_3d(sbase + C::oV + st * 8192, &tm_v, bar(bVF + st), n * 64, 0, bhkv);
                 bulk_load(sbase + C::oSfV + st * 1024, p.v_sf + ((size_t)bhkv * p.nkb + n) * C::kSfVBytes,
@@ -263,8 +260,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 for (int ks = 0; ks < D / 64; ++ks)
                     tc_mma_nvfp4(tmem + (bb ? C::cS1 : C::cS0), q_desc + 2 * ks, k_desc + 2 * ks, idesc_qk,
                                  tmem + C::cSfQ + 4 * ks, tmem + C::cSfK + 4 * ks, true);
-                tc_commit(bar(bKE + st));
-                tc_commit(bar(bSF + bb));
+                tc_commit(bar(bQK + st));
                 return true;
             };
             PT_DECL
@@ -307,9 +303,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 for (int ks = 0; ks < 2; ++ks)
                     tc_mma_nvfp4(tmem + C::cO, p_desc + 2 * ks, v_desc + 2 * ks, idesc_pv, tmem + C::cSfP + 4 * ks,
                                  tmem + C::cSfV + 4 * ks, (j > 0) || (ks > 0));
-                tc_commit(bar(bVE + st));
-                tc_commit(bar(bPE + bb));
-                tc_commit(bar(bOR));
+                tc_commit(bar(bPV + st));
                 PT(4)
             }
             PT_DUMP(2)
@@ -402,7 +396,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (p.debug != nullptr && blockIdx.x == 0 && j == 0) p.debug[16384 + 128 + r] = rowsum;
             PT(0)
             // P buffer `par` was last read by the PV MMA of block j - 2
-            if (j >= 2 && !warp_wait(bar(bPE + par), ((j >> 1) - 1) & 1, abort_flag, p.status, kWaitPEmpty)) { alive = false; break; }
+            if (j >= 2 && !warp_wait(bar(bPV + (j - 2) % S), ((j - 2) / S) & 1, abort_flag, p.status, kWaitPEmpty)) { alive = false; break; }
             // P codes: four 16-byte chunks of the 64-byte-swizzled K-major row; scales: one word per 64-key atom
 #pragma unroll
             for (int c = 0; c < 4; ++c)
@@ -441,7 +435,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // statistics of block j: constants into shared memory, rescale factor returned
         auto do_stats = [&](int j, float& alpha_out) -> bool {
             const int n = nb - 1 - j, bb = j & 1;
-            if (!warp_wait(bar(bSF + bb), (j >> 1) & 1, abort_flag, p.status, kWaitSFull)) return false;
+            if (!warp_wait(bar(bQK + j % S), (j / S) & 1, abort_flag, p.status, kWaitSFull)) return false;
             PT(0)
             tc_fence_after();
             const bool need_mask = ((n + 1) * kBlock > p.Nk) || (CAUSAL && (n * kBlock + kBlock - 1 > mt * kBlock + shift));
@@ -501,7 +495,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             float alpha_next = 1.f;
             if (j + 1 < nb && !do_stats(j + 1, alpha_next)) { alive = false; break; }
             if (j > 0) {
-                if (!warp_wait(bar(bOR), (j - 1) & 1, abort_flag, p.status, kWaitOReady)) { alive = false; break; }
+                if (!warp_wait(bar(bPV + (j - 1) % S), ((j - 1) / S) & 1, abort_flag, p.status, kWaitOReady)) { alive = false; break; }
                 PT(3)
                 if (__any_sync(0xffffffffu, alpha != 1.0f)) {
                     tc_fence_after();
@@ -535,7 +529,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             float l_tot = 0.f;
             if (nb > 0) {
                 alive = warp_wait(bar(bLR), 0, abort_flag, p.status, kWaitAlpha);
-                if (alive) alive = warp_wait(bar(bOR), (nb - 1) & 1, abort_flag, p.status, kWaitOReady);
+                if (alive) alive = warp_wait(bar(bPV + (nb - 1) % S), ((nb - 1) / S) & 1, abort_flag, p.status, kWaitOReady);
                 if (alive) {
                     tc_fence_after();
                     // each exp warpgroup's sum refers to the maximum of its own last block: bring both to the final one
