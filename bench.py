@@ -226,6 +226,7 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")    # keep stdout for the one JSON line
         dist.init_process_group("nccl", device_id=dev)
 
     # seeded synthetic input, generated on the device in chunks (the full tensors are several GB)
