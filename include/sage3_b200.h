@@ -138,6 +138,14 @@ SAGE3_API int sage3_check_status(const void* ws, int32_t* word, void* stream);
 SAGE3_API int sage3_attn_fwd_debug(const Sage3Desc* desc, void* ws, void* out, float* debug, void* stream);
 
 /*
+ * Failure-reporting self test: launches one warp that waits, with a limit of about a millisecond, on a barrier
+ * nobody arrives on.  The kernel returns normally; afterwards sage3_check_status(ws, &word, stream) must report
+ * SAGE3_E_DEVICE_WAIT with word == 199.  `ws` needs 256 bytes.  No counterpart in the reference (its only failure
+ * handling is `assert` and `exit`, quantization/cuda_utils.h:19-27).
+ */
+SAGE3_API int sage3_selftest_wait_timeout(void* ws, void* stream);
+
+/*
  * Mean of K over its Nk tokens, per (batch, kv-head) and channel -- the first stage of the pre-pass -- for
  * callers that must not allocate device memory and cannot hand over a workspace: for instance a serving
  * engine that gave all device memory to its own pool at start-up, or a latency-critical loop in which a

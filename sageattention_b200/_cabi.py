@@ -68,6 +68,8 @@ def lib() -> C.CDLL:
     l.sage3_attn_fwd_debug.argtypes = [P(Sage3Desc), V, V, V, V]
     l.sage3_fwd.restype = C.c_int
     l.sage3_fwd.argtypes = [P(Sage3Desc), V, V, V, V, V, V, V]
+    l.sage3_selftest_wait_timeout.restype = C.c_int
+    l.sage3_selftest_wait_timeout.argtypes = [V, V]
     l.sage3_kmean_noalloc.restype = C.c_int
     l.sage3_kmean_noalloc.argtypes = [P(Sage3Desc), V, V, V]
     l.sage3_check_status.restype = C.c_int
@@ -77,7 +79,7 @@ def lib() -> C.CDLL:
 
 
 EXPORTED = ["sage3_version", "sage3_strerror", "sage3_workspace_layout", "sage3_workspace_bytes", "sage3_prepass",
-            "sage3_attn_fwd", "sage3_fwd", "sage3_check_status", "sage3_attn_fwd_debug", "sage3_kmean_noalloc"]
+            "sage3_attn_fwd", "sage3_fwd", "sage3_check_status", "sage3_attn_fwd_debug", "sage3_kmean_noalloc", "sage3_selftest_wait_timeout"]
 
 
 def check(code: int, where: str) -> None:

@@ -102,6 +102,20 @@ int attn_impl(const Sage3Desc* desc, void* ws, void* out, float* lse, float* deb
     return sage3::launch_attn(a, st, &drv) == cudaSuccess ? SAGE3_OK : SAGE3_E_CUDA;
 }
 
+// One warp waits on a barrier that nobody ever arrives on, with a limit of about a millisecond: exercises the
+// bounded-wait path (status word, abort flag, normal kernel exit) without hanging anything.
+__global__ void wait_timeout_selftest_kernel(int* status) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        sage3::mbar_init(sage3::smem_u32(&bar), 1);
+        sage3::mbar_fence_init();
+    }
+    __syncthreads();
+    sage3::mbar_wait(sage3::smem_u32(&bar), 0, &abort_flag, status, sage3::kWaitSelfTest, 2000000LL);
+}
+
 }  // namespace
 
 extern "C" {
@@ -174,6 +188,16 @@ SAGE3_API int sage3_fwd(const Sage3Desc* desc, const void* q, const void* k, con
     const int rc = sage3_prepass(desc, q, k, v, ws, stream);
     if (rc != SAGE3_OK) return rc;
     return sage3_attn_fwd(desc, ws, out, lse, stream);
+}
+
+SAGE3_API int sage3_selftest_wait_timeout(void* ws, void* stream) {
+    if (!ws) return SAGE3_E_NULL;
+    const int rc = check_arch();
+    if (rc != SAGE3_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(ws, 0, 64 * sizeof(int32_t), st) != cudaSuccess) return SAGE3_E_CUDA;
+    wait_timeout_selftest_kernel<<<1, 32, 0, st>>>(static_cast<int*>(ws));
+    return cudaGetLastError() == cudaSuccess ? SAGE3_OK : SAGE3_E_CUDA;
 }
 
 SAGE3_API int sage3_check_status(const void* ws, int32_t* word, void* stream) {

@@ -16,7 +16,7 @@ constexpr int kMicro = 16;    // NVFP4 microblock
 enum : int {
     kWaitQFull = 101, kWaitKFull = 102, kWaitVFull = 103, kWaitKEmpty = 104, kWaitVEmpty = 105,
     kWaitSFull = 106, kWaitSEmpty = 107, kWaitPFull = 108, kWaitOReady = 109, kWaitPair = 110,
-    kWaitDelta = 111, kWaitOScaled = 112, kWaitPEmpty = 113, kWaitAlpha = 114, kWaitStats = 115
+    kWaitDelta = 111, kWaitOScaled = 112, kWaitPEmpty = 113, kWaitAlpha = 114, kWaitStats = 115, kWaitSelfTest = 199
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -156,7 +156,7 @@ constexpr long long kWaitLimitCycles = 2000000000LL;   // about a second
 // from the math warps of the same scheduler).
 template <bool kBackoff = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status_word, int code) {
+                                          int* status_word, int code, long long limit_cycles = kWaitLimitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t spins = 0;
@@ -165,7 +165,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (kBackoff) __nanosleep(40);
         if ((++spins & 0x3f) == 0) {
             if (*abort_flag != 0) return false;
-            if (clock64() - t0 > kWaitLimitCycles || *reinterpret_cast<volatile int*>(status_word) != 0) {
+            if (clock64() - t0 > limit_cycles || *reinterpret_cast<volatile int*>(status_word) != 0) {
                 atomicCAS(status_word, 0, code);
                 *abort_flag = 1;
                 return false;

@@ -91,3 +91,20 @@ def test_sampled_rows_at_length_8k(cuda_device):
         ref = O.attention_from_prepass(pp, q_rows=rows)
         got = out[:, :, rows]
         assert O.cosine(got, ref) >= COS_MIN and O.rel_l1(got, ref) <= RELL1_MAX
+
+
+def test_bounded_wait_reports_instead_of_hanging(cuda_device):
+    """A wait that can never be satisfied ends after its limit, the kernel exits normally, and the host reads the
+    reason from the status word; the context stays usable (the next launch works)."""
+    import ctypes as C
+    from sageattention_b200 import _cabi
+    ws = torch.zeros(256, dtype=torch.uint8, device=cuda_device)
+    stream = torch.cuda.current_stream(cuda_device).cuda_stream
+    assert _cabi.lib().sage3_selftest_wait_timeout(ws.data_ptr(), stream) == 0
+    word = C.c_int32(0)
+    rc = _cabi.lib().sage3_check_status(ws.data_ptr(), C.byref(word), stream)
+    assert rc == _cabi.SAGE3_E_DEVICE_WAIT and word.value == 199
+    q, k, v = (t.to(cuda_device) for t in O.make_inputs(1, 1, 1, 128, 128, 64, seed=3))
+    out = sageattn3(q, k, v)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
