@@ -226,8 +226,18 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")    # keep stdout for the one JSON line
-        dist.init_process_group("nccl", device_id=dev)
+        # NCCL prints its version banner to stdout while the communicator is created; stdout is for the one
+        # JSON line, so file descriptor 1 points at stderr until the first collective has completed
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=dev)
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
 
     # seeded synthetic input, generated on the device in chunks (the full tensors are several GB)
     g = torch.Generator(device=dev).manual_seed(2000 + rank)
