@@ -145,7 +145,7 @@ __device__ __forceinline__ void mma16816<__half>(float* c, const uint32_t* a, ui
 }
 
 template <typename T, int D, int MODE>
-__global__ void __launch_bounds__(256) quant_rows_kernel(
+__global__ void __launch_bounds__(256, 3) quant_rows_kernel(
     const T* __restrict__ x, int64_t sb, int64_t sh, int64_t sn, int H, int N, int Np,
     const T* __restrict__ mean_in,     // K: km [B*H][D]; Q global mean: qm [B*H][D]; unused for block mean
     T* __restrict__ qm_out,            // Q block mean: [B*H][Np/128][D]
@@ -359,16 +359,24 @@ __global__ void __launch_bounds__(256) quant_vt_kernel(const T* __restrict__ x, 
         dst[0] = val.x; dst[1] = val.y; dst[2] = val.z; dst[3] = val.w;
     }
     __syncthreads();
-    // microblock (channel d, token group mb): channel fastest across threads
-    for (int item = t; item < D * 8; item += 256) {
-        const int d = item % D, mb = item / D;
-        float y[16];
+    // two microblocks per item: (channels 2*dp and 2*dp + 1, token group mb); channel pair fastest across
+    // threads, so every shared-memory read is one conflict-free 32-bit word holding both channels
+    for (int item = t; item < (D / 2) * 8; item += 256) {
+        const int dp = item % (D / 2), mb = item / (D / 2);
+        float y0[16], y1[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) y[i] = Num<T>::to_f(s_v[(mb * 16 + i) * PITCH + d]);
+        for (int i = 0; i < 16; ++i) {
+            const float2 v2 = Num<T>::to_f2(*reinterpret_cast<const uint32_t*>(s_v + (mb * 16 + i) * PITCH + 2 * dp));
+            y0[i] = v2.x;
+            y1[i] = v2.y;
+        }
         uint32_t lo, hi, sfb;
-        quant16(y, lo, hi, sfb);
-        *reinterpret_cast<uint2*>(s_out + d * OPITCH + mb * 8) = make_uint2(lo, hi);
-        s_sf[sf_atom_offset(d, mb)] = static_cast<uint8_t>(sfb);
+        quant16(y0, lo, hi, sfb);
+        *reinterpret_cast<uint2*>(s_out + (2 * dp) * OPITCH + mb * 8) = make_uint2(lo, hi);
+        s_sf[sf_atom_offset(2 * dp, mb)] = static_cast<uint8_t>(sfb);
+        quant16(y1, lo, hi, sfb);
+        *reinterpret_cast<uint2*>(s_out + (2 * dp + 1) * OPITCH + mb * 8) = make_uint2(lo, hi);
+        s_sf[sf_atom_offset(2 * dp + 1, mb)] = static_cast<uint8_t>(sfb);
     }
     __syncthreads();
     // coalesced stores: D rows of 64 bytes
