@@ -367,27 +367,50 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             uint32_t codes[16];
             uint32_t sfb[2] = {0, 0};
             float rowsum = 0.f;
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                // E = P~ / sf = 6 * 2^((S - bm) s)  with  negc = -(bm s - log2 6)
-                const uint64_t negc2 = pack2f(negc[g], negc[g]);
-                float e[16];
-                uint64_t acc0 = 0, acc1 = 0;      // two packed partial sums (bit pattern of +0.0f pairs)
+            // Software pipeline over the eight microblocks: the exp2 instructions of microblock g + 1 are issued
+            // before the sums / conversions of microblock g, so the exp2 unit always has work queued.
+            // E = P~ / sf = 6 * 2^((S - bm) s)  with  negc = -(bm s - log2 6)
+            float e[16];
+            {
+                const uint64_t negc2 = pack2f(negc[0], negc[0]);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     float a, b2;
-                    unpack2f(fma2(pack2f(s[16 * g + 2 * i], s[16 * g + 2 * i + 1]), sl2x2, negc2), a, b2);
+                    unpack2f(fma2(pack2f(s[2 * i], s[2 * i + 1]), sl2x2, negc2), a, b2);
                     e[2 * i] = ex2_approx(a);
                     e[2 * i + 1] = ex2_approx(b2);
-                    if (i & 1) acc1 = add2(acc1, pack2f(e[2 * i], e[2 * i + 1]));
-                    else acc0 = add2(acc0, pack2f(e[2 * i], e[2 * i + 1]));
                 }
+            }
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                float en[16];
+                if (g < 7) {
+                    const uint64_t negc2 = pack2f(negc[g + 1], negc[g + 1]);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        float a, b2;
+                        unpack2f(fma2(pack2f(s[16 * (g + 1) + 2 * i], s[16 * (g + 1) + 2 * i + 1]), sl2x2, negc2), a, b2);
+                        en[2 * i] = ex2_approx(a);
+                        en[2 * i + 1] = ex2_approx(b2);
+                    }
+                }
+                uint64_t acc0 = pack2f(e[0], e[1]), acc1 = pack2f(e[2], e[3]);
+                acc0 = add2(acc0, pack2f(e[4], e[5]));
+                acc1 = add2(acc1, pack2f(e[6], e[7]));
+                acc0 = add2(acc0, pack2f(e[8], e[9]));
+                acc1 = add2(acc1, pack2f(e[10], e[11]));
+                acc0 = add2(acc0, pack2f(e[12], e[13]));
+                acc1 = add2(acc1, pack2f(e[14], e[15]));
                 float se0, se1;
                 unpack2f(add2(acc0, acc1), se0, se1);
                 rowsum = fmaf(sfv[g], se0 + se1, rowsum);
                 codes[2 * g] = cvt_e2m1x8(e[0], e[1], e[2], e[3], e[4], e[5], e[6], e[7]);
                 codes[2 * g + 1] = cvt_e2m1x8(e[8], e[9], e[10], e[11], e[12], e[13], e[14], e[15]);
                 sfb[g >> 2] |= (cvt_e4m3x2(sfv[g], 0.f) & 0xffu) << (8 * (g & 3));
+                if (g < 7) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) e[i] = en[i];
+                }
             }
             // row sum relative to the running maximum of this block: rescale what this warpgroup has so far
             const float a_eff = (l_run == 0.f) ? 0.f : ex2_approx(ms_prev - ms);
