@@ -172,6 +172,8 @@ SAGE3_API int sage3_prepass(const Sage3Desc* desc, const void* q, const void* k,
     a.q_codes = base + w.q_codes; a.q_sf = base + w.q_sf;
     a.k_codes = base + w.k_codes; a.k_sf = base + w.k_sf;
     a.v_codes = base + w.v_codes; a.v_sf = base + w.v_sf;
+    a.status = reinterpret_cast<int*>(base + w.status);
+    if (cudaMemsetAsync(base + w.status, 0, 64 * sizeof(int32_t), static_cast<cudaStream_t>(stream)) != cudaSuccess) return SAGE3_E_CUDA;
     return sage3::launch_prepass(a, static_cast<cudaStream_t>(stream)) == cudaSuccess ? SAGE3_OK : SAGE3_E_CUDA;
 }
 

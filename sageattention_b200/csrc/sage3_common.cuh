@@ -16,7 +16,7 @@ constexpr int kMicro = 16;    // NVFP4 microblock
 enum : int {
     kWaitQFull = 101, kWaitKFull = 102, kWaitVFull = 103, kWaitKEmpty = 104, kWaitVEmpty = 105,
     kWaitSFull = 106, kWaitSEmpty = 107, kWaitPFull = 108, kWaitOReady = 109, kWaitPair = 110,
-    kWaitDelta = 111, kWaitOScaled = 112, kWaitPEmpty = 113, kWaitAlpha = 114, kWaitStats = 115, kWaitSelfTest = 199
+    kWaitDelta = 111, kWaitOScaled = 112, kWaitPEmpty = 113, kWaitAlpha = 114, kWaitStats = 115, kWaitDeltaMma = 116, kWaitSelfTest = 199
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -251,6 +251,12 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uin
 //   (0 = K, 1 = MN), bits 17-22: N >> 3, bits 24-28: M >> 4.
 __host__ __device__ constexpr uint32_t make_idesc_f16_bmn(int n, bool bf16) {
     return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | (1u << 16) |
+           (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+}
+
+// same, both operands K-major
+__host__ __device__ constexpr uint32_t make_idesc_f16_kk(int n, bool bf16) {
+    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) |
            (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
 }
 

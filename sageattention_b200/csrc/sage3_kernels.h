@@ -17,6 +17,7 @@ struct PrepassArgs {
     float* kpart;
     void *km, *qm, *delta;
     uint8_t *q_codes, *q_sf, *k_codes, *k_sf, *v_codes, *v_sf;
+    int* status;                   // device status words (bounded waits report here)
 };
 
 struct AttnArgs {

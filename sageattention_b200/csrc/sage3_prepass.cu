@@ -5,7 +5,7 @@
 // Math follows (paths inside the reference project, sageattention3_blackwell/sageattn3/...):
 //   api.py:84            k' = k - mean_N(k)                 (mean: fp32 sum, rounded to the input type)
 //   api.py:55-72, 86-90  q' = q - mean of each 128-row block (or of all padded rows)
-//   api.py:91            delta_s = qm . k'^T, rounded to the input type
+//   api.py:91            delta_s = qm . k'^T, rounded to the input type (tcgen05 16-bit MMA, accumulator in TMEM)
 //   quantization/fp4_quantization_4d.cu:185-225   SF = e4m3(amax / 6), code = e2m1(x * (1 / SF))
 //   quantization/fp4_quantization_4d.cu:300-349   V: microblocks are 16 consecutive tokens of one channel
 // Divisions and reciprocals are IEEE (div.rn / rcp.rn) so the result can be checked bit for bit.
@@ -20,6 +20,7 @@ namespace sage3 {
 template <typename T> struct Num;
 template <> struct Num<__nv_bfloat16> {
     using T2 = __nv_bfloat162;
+    static constexpr bool kIsBf16 = true;
     static __device__ __forceinline__ float to_f(__nv_bfloat16 x) { return __bfloat162float(x); }
     static __device__ __forceinline__ __nv_bfloat16 from_f(float x) { return __float2bfloat16_rn(x); }
     static __device__ __forceinline__ float2 to_f2(uint32_t w) {
@@ -28,6 +29,7 @@ template <> struct Num<__nv_bfloat16> {
 };
 template <> struct Num<__half> {
     using T2 = __half2;
+    static constexpr bool kIsBf16 = false;
     static __device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
     static __device__ __forceinline__ __half from_f(float x) { return __float2half_rn(x); }
     static __device__ __forceinline__ float2 to_f2(uint32_t w) {
@@ -121,45 +123,20 @@ __global__ void colmean_finalize_kernel(const float* __restrict__ part, int chun
 }
 
 // ------------------------------------------------------------------------------------------------
-// Q / K: smooth + quantize one 128-row tile per CTA; K tiles also produce their delta_s columns
+// Q: smooth + quantize one 128-row tile per CTA
 // ------------------------------------------------------------------------------------------------
-enum { kModeQBlockMean = 0, kModeQGlobalMean = 1, kModeK = 2 };
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-template <typename T>
-__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1);
-template <>
-__device__ __forceinline__ void mma16816<__nv_bfloat16>(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-template <>
-__device__ __forceinline__ void mma16816<__half>(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
+enum { kModeQBlockMean = 0, kModeQGlobalMean = 1 };
 
 template <typename T, int D, int MODE>
 __global__ void __launch_bounds__(256, 3) quant_rows_kernel(
     const T* __restrict__ x, int64_t sb, int64_t sh, int64_t sn, int H, int N, int Np,
-    const T* __restrict__ mean_in,     // K: km [B*H][D]; Q global mean: qm [B*H][D]; unused for block mean
-    T* __restrict__ qm_out,            // Q block mean: [B*H][Np/128][D]
+    const T* __restrict__ mean_in,     // one mean per head: qm [B*H][D]; unused for block mean
+    T* __restrict__ qm_out,            // block mean: [B*H][Np/128][D]
     uint8_t* __restrict__ codes,       // [B*H][Np][D/2]
-    uint8_t* __restrict__ sfs,         // [B*H][Np/128][D/64][512]
-    // K mode only: delta_s
-    const T* __restrict__ qm_all,      // [B][Hq][nqm][D]
-    T* __restrict__ delta,             // [B][Hq][nqm][Np]
-    int Hq, int nqm) {
+    uint8_t* __restrict__ sfs) {       // [B*H][Np/128][D/64][512]
     constexpr int CH = D / 16;            // microblocks per row
     constexpr int RPP = 256 / CH;         // rows per pass
     constexpr int ITEMS = kBlock / RPP;   // microblocks per thread
-    constexpr int PITCH = D + 8;          // smem row pitch in elements (odd multiple of 16 bytes)
-    constexpr int MCH = 64;               // query blocks per delta_s pass
 
     const int tile = blockIdx.x, bh = blockIdx.y;
     const int b = bh / H, h = bh % H;
@@ -172,10 +149,6 @@ __global__ void __launch_bounds__(256, 3) quant_rows_kernel(
     float* s_mean = reinterpret_cast<float*>(smem_raw);                        // [D]
     uint8_t* s_sf = smem_raw + D * 4;                                          // [(D/64) * 512]
     float* s_red = reinterpret_cast<float*>(s_sf + (D / 64) * 512);            // [8 warps][D] (block mean)
-    T* s_k = reinterpret_cast<T*>(reinterpret_cast<uint8_t*>(s_red) + 8 * D * 4);   // [128][PITCH]  (K mode)
-    T* s_a = s_k + kBlock * PITCH;                                                  // [MCH][PITCH] (K mode)
-    constexpr int DPITCH = kBlock + 8;    // staging pitch of a 128-key delta_s row
-    T* s_d = s_a + MCH * PITCH;                                                     // [MCH][DPITCH] (K mode) delta_s staging
 
     uint4 raw[ITEMS][2];
 #pragma unroll
@@ -231,24 +204,13 @@ __global__ void __launch_bounds__(256, 3) quant_rows_kernel(
         const int r = row0 + rt;
         float y[16];
         unpack16<T>(raw[i][0], raw[i][1], y);
-        const bool zero_row = (MODE == kModeK) && (r >= N);   // K is padded after smoothing: pad rows are 0
+        // rows beyond N hold 0 - mean (Q is padded before smoothing); they are never read back
 #pragma unroll
-        for (int j = 0; j < 16; ++j) y[j] = zero_row ? 0.f : Num<T>::to_f(Num<T>::from_f(y[j] - mu[j]));
+        for (int j = 0; j < 16; ++j) y[j] = Num<T>::to_f(Num<T>::from_f(y[j] - mu[j]));
         uint32_t lo, hi, sfb;
         quant16(y, lo, hi, sfb);
         *reinterpret_cast<uint2*>(codes + ((int64_t)bh * Np + r) * (D / 2) + c * 8) = make_uint2(lo, hi);
         s_sf[sf_atom_offset(rt, c)] = static_cast<uint8_t>(sfb);
-        if (MODE == kModeK) {
-            // keep k' for the delta_s product
-            typename Num<T>::T2* dst = reinterpret_cast<typename Num<T>::T2*>(s_k + rt * PITCH + c * 16);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                typename Num<T>::T2 p;
-                p.x = Num<T>::from_f(y[2 * j]);
-                p.y = Num<T>::from_f(y[2 * j + 1]);
-                dst[j] = p;
-            }
-        }
     }
     __syncthreads();
     // scale factors of the tile: (D/64) atoms of 512 bytes, contiguous
@@ -256,74 +218,173 @@ __global__ void __launch_bounds__(256, 3) quant_rows_kernel(
         uint8_t* dst = sfs + ((int64_t)bh * (Np / kBlock) + tile) * (D / 64) * 512;
         if (t < (D / 64) * 32) reinterpret_cast<uint4*>(dst)[t] = reinterpret_cast<const uint4*>(s_sf)[t];
     }
+}
 
-    if (MODE == kModeK) {
-        // delta_s[b][hq][qb][row0 + n] = sum_d qm[b][hq][qb][d] * k'[n][d] for every query head of this kv head
-        const int group = Hq / H;
-        const int warp = t >> 5, lane = t & 31;
-        const uint32_t sk_addr = smem_u32(s_k), sa_addr = smem_u32(s_a);
-        for (int g = 0; g < group; ++g) {
-            const int hq = h * group + g;
-            const T* qmh = qm_all + ((int64_t)b * Hq + hq) * nqm * D;
-            T* dh = delta + ((int64_t)b * Hq + hq) * nqm * (int64_t)Np;
-            for (int m0 = 0; m0 < nqm; m0 += MCH) {
-                __syncthreads();   // previous pass done with s_a
-                for (int idx = t; idx < MCH * (D / 8); idx += 256) {
-                    const int r = idx / (D / 8), c8 = idx % (D / 8);
-                    uint4 val = make_uint4(0, 0, 0, 0);
-                    if (m0 + r < nqm) val = __ldg(reinterpret_cast<const uint4*>(qmh + (int64_t)(m0 + r) * D + c8 * 8));
-                    *reinterpret_cast<uint4*>(s_a + r * PITCH + c8 * 8) = val;
-                }
-                __syncthreads();
-                float acc[MCH / 16][2][4];
+// ------------------------------------------------------------------------------------------------
+// K: smooth + quantize one 128-key tile per CTA, and its delta_s columns on the tensor core:
+// delta_s[qb][key] = sum_d qm[qb][d] * k'[key][d] as 128 x 128 x D tcgen05 MMAs (16-bit operands from shared
+// memory in the 128-byte-swizzled K-major layout, fp32 accumulator in tensor memory), one per 128 query blocks.
+// ------------------------------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
+    const T* __restrict__ x, int64_t sb, int64_t sh, int64_t sn, int H, int N, int Np,
+    const T* __restrict__ km,          // [B*H][D]
+    uint8_t* __restrict__ codes,       // [B*H][Np][D/2]
+    uint8_t* __restrict__ sfs,         // [B*H][Np/128][D/64][512]
+    const T* __restrict__ qm_all,      // [B][Hq][nqm][D]
+    T* __restrict__ delta,             // [B][Hq][nqm][Np]
+    int Hq, int nqm, int* __restrict__ status) {
+    constexpr int CH = D / 16;            // microblocks per row
+    constexpr int RPP = 256 / CH;         // rows per pass
+    constexpr int ITEMS = kBlock / RPP;   // microblocks per thread
+    constexpr int SUB = D / 64;           // 64-element (128-byte) sub-tiles along K
+    constexpr uint32_t kTmemCols = 128;
+    constexpr bool kBf16 = sizeof(T) == 2 && Num<T>::kIsBf16;
+
+    const int tile = blockIdx.x, bh = blockIdx.y;
+    const int b = bh / H, h = bh % H;
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int c = t % CH, rl = t / CH;
+    const T* base = x + b * sb + h * sh;
+    const int row0 = tile * kBlock;
+
+    extern __shared__ uint8_t smem_dyn[];
+    const uint32_t sbase = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    uint8_t* sgen = smem_dyn + (sbase - smem_u32(smem_dyn));
+    // [B tile: k' | A tile: qm chunk] as SUB sub-tiles of 128 rows x 128 bytes each, then small things
+    constexpr int oB = 0, oA = SUB * 16384, oMean = 2 * SUB * 16384, oSf = oMean + D * 4, oBar = oSf + SUB * 512;
+    float* s_mean = reinterpret_cast<float*>(sgen + oMean);
+    uint8_t* s_sf = sgen + oSf;
+    const uint32_t bar = sbase + oBar;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + oBar + 8);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + oBar + 12);
+
+    if (t == 0) {
+        *abort_flag = 0;
+        mbar_init(bar, 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    uint4 raw[ITEMS][2];
 #pragma unroll
-                for (int mt = 0; mt < MCH / 16; ++mt)
+    for (int i = 0; i < ITEMS; ++i) {
+        const int r = row0 + rl + RPP * i;
+        load16_packed<T>(base + (int64_t)r * sn + c * 16, r < N, raw[i][0], raw[i][1]);
+    }
+    if (t < D) s_mean[t] = Num<T>::to_f(km[(int64_t)bh * D + t]);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    float mu[16];
 #pragma unroll
-                    for (int nt = 0; nt < 2; ++nt)
+    for (int j = 0; j < 16; ++j) mu[j] = s_mean[c * 16 + j];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) acc[mt][nt][e] = 0.f;
+    for (int i = 0; i < ITEMS; ++i) {
+        const int rt = rl + RPP * i;          // row inside the tile
+        const int r = row0 + rt;
+        float y[16];
+        unpack16<T>(raw[i][0], raw[i][1], y);
+        const bool zero_row = (r >= N);       // K is padded after smoothing: pad rows are 0
+#pragma unroll
+        for (int j = 0; j < 16; ++j) y[j] = zero_row ? 0.f : Num<T>::to_f(Num<T>::from_f(y[j] - mu[j]));
+        uint32_t lo, hi, sfb;
+        quant16(y, lo, hi, sfb);
+        *reinterpret_cast<uint2*>(codes + ((int64_t)bh * Np + r) * (D / 2) + c * 8) = make_uint2(lo, hi);
+        s_sf[sf_atom_offset(rt, c)] = static_cast<uint8_t>(sfb);
+        // k' into the B tile: this item's 16 elements are the 16-byte chunks 2c, 2c+1 of row rt
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            typename Num<T>::T2 pr;
+            pr.x = Num<T>::from_f(y[2 * j]);
+            pr.y = Num<T>::from_f(y[2 * j + 1]);
+            w[j] = *reinterpret_cast<uint32_t*>(&pr);
+        }
+#pragma unroll
+        for (int q2 = 0; q2 < 2; ++q2) {
+            const int chunk = 2 * c + q2, sub = chunk >> 3, cw = chunk & 7;
+            *reinterpret_cast<uint4*>(sgen + oB + sub * 16384 + rt * 128 + ((cw ^ (rt & 7)) << 4)) =
+                make_uint4(w[4 * q2], w[4 * q2 + 1], w[4 * q2 + 2], w[4 * q2 + 3]);
+        }
+    }
+    __syncthreads();
+    {
+        uint8_t* dst = sfs + ((int64_t)bh * (Np / kBlock) + tile) * (D / 64) * 512;
+        if (t < (D / 64) * 32) reinterpret_cast<uint4*>(dst)[t] = reinterpret_cast<const uint4*>(s_sf)[t];
+    }
+
+    // delta_s for every query head of this kv head, 128 query blocks per MMA group
+    constexpr uint32_t idesc = make_idesc_f16_kk(128, kBf16);
+    const int group = Hq / H;
+    const int quarter = warp & 3, chalf = warp >> 2;       // tensor-memory lane quarter, column half of the epilogue
+    uint32_t iter = 0;
+    bool alive = true;
+    for (int g = 0; g < group && alive; ++g) {
+        const int hq = h * group + g;
+        const T* qmh = qm_all + ((int64_t)b * Hq + hq) * nqm * D;
+        T* dh = delta + ((int64_t)b * Hq + hq) * nqm * (int64_t)Np;
+        for (int m0 = 0; m0 < nqm && alive; m0 += 128, ++iter) {
+            // A tile: 128 query-block means, same swizzled layout
+            for (int idx = t; idx < 128 * (D / 8); idx += 256) {
+                const int r = idx / (D / 8), chunk = idx % (D / 8);
+                uint4 val = make_uint4(0, 0, 0, 0);
+                if (m0 + r < nqm) val = __ldg(reinterpret_cast<const uint4*>(qmh + (int64_t)(m0 + r) * D + chunk * 8));
+                *reinterpret_cast<uint4*>(sgen + oA + (chunk >> 3) * 16384 + r * 128 + (((chunk & 7) ^ (r & 7)) << 4)) = val;
+            }
+            fence_proxy_async_smem();
+            tc_fence_before();
+            __syncthreads();
+            if (t == 0) {
+                tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
-                    uint32_t bf[4];
-                    {   // B: keys [16 * warp, +16), k [16 * ks, +16): matrices (n-tile, k-half)
-                        const int i = lane >> 3;
-                        const int n = warp * 16 + (lane & 7) + 8 * (i >> 1);
-                        const int kk = ks * 16 + 8 * (i & 1);
-                        ldmatrix_x4(sk_addr + (n * PITCH + kk) * 2, bf[0], bf[1], bf[2], bf[3]);
-                    }
-#pragma unroll
-                    for (int mt = 0; mt < MCH / 16; ++mt) {
-                        uint32_t af[4];
-                        const int i = lane >> 3;
-                        const int r = mt * 16 + (lane & 7) + 8 * (i & 1);
-                        const int kk = ks * 16 + 8 * (i >> 1);
-                        ldmatrix_x4(sa_addr + (r * PITCH + kk) * 2, af[0], af[1], af[2], af[3]);
-                        mma16816<T>(acc[mt][0], af, bf[0], bf[1]);
-                        mma16816<T>(acc[mt][1], af, bf[2], bf[3]);
-                    }
+                    const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
+                    tc_mma_f16(tmem, make_sdesc(sbase + oA + off, 16, 1024, kSwz128), make_sdesc(sbase + oB + off, 16, 1024, kSwz128),
+                               idesc, ks > 0);
                 }
-                // stage the 64 x 128 result in shared memory, then write whole 256-byte rows
+                tc_commit(bar);
+            }
+            alive = mbar_wait(bar, iter & 1, abort_flag, status, kWaitDeltaMma);
+            alive = __syncthreads_and(alive ? 1 : 0) != 0;
+            if (!alive) break;
+            tc_fence_after();
+            // epilogue: thread = query block (row), 64 keys of its row -> 128 contiguous bytes
+            const int qb = m0 + quarter * 32 + lane;
 #pragma unroll
-                for (int mt = 0; mt < MCH / 16; ++mt)
+            for (int cc = 0; cc < 2; ++cc) {
+                float v[32];
+                tmem_ld32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + chalf * 64 + cc * 32, v);
+                tc_wait_ld();
+                if (qb < nqm) {
+                    T* drow = dh + (int64_t)qb * Np + row0 + chalf * 64 + cc * 32;
 #pragma unroll
-                    for (int nt = 0; nt < 2; ++nt)
+                    for (int i = 0; i < 4; ++i) {
+                        uint32_t p4[4];
 #pragma unroll
-                        for (int half = 0; half < 2; ++half) {
-                            typename Num<T>::T2 p;
-                            p.x = Num<T>::from_f(acc[mt][nt][2 * half]);
-                            p.y = Num<T>::from_f(acc[mt][nt][2 * half + 1]);
-                            *reinterpret_cast<typename Num<T>::T2*>(s_d + (mt * 16 + (lane >> 2) + 8 * half) * DPITCH + warp * 16 +
-                                                                    nt * 8 + 2 * (lane & 3)) = p;
+                        for (int e = 0; e < 4; ++e) {
+                            typename Num<T>::T2 pr;
+                            pr.x = Num<T>::from_f(v[8 * i + 2 * e]);
+                            pr.y = Num<T>::from_f(v[8 * i + 2 * e + 1]);
+                            p4[e] = *reinterpret_cast<uint32_t*>(&pr);
                         }
-                __syncthreads();
-                for (int idx = t; idx < MCH * 16; idx += 256) {
-                    const int rr = idx >> 4, c16 = idx & 15;
-                    if (m0 + rr < nqm)
-                        *reinterpret_cast<uint4*>(dh + (int64_t)(m0 + rr) * Np + row0 + c16 * 8) =
-                            *reinterpret_cast<const uint4*>(s_d + rr * DPITCH + c16 * 8);
+                        *reinterpret_cast<uint4*>(drow + 8 * i) = make_uint4(p4[0], p4[1], p4[2], p4[3]);
+                    }
                 }
             }
+            tc_fence_before();
+            __syncthreads();      // the accumulator and the A tile are free again
         }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
     }
 }
 
@@ -410,10 +471,9 @@ static cudaError_t launch_prepass_t(const PrepassArgs& a, cudaStream_t st) {
     colmean_finalize_kernel<T, D><<<BHkv, D, 0, st>>>(a.kpart, a.kchunks_k, 1.0f / (float)a.Nk, km);
 
     const size_t smem_q = D * 4 + (D / 64) * 512 + 8 * D * 4;
-    const size_t smem_k = smem_q + (size_t)(kBlock + 64) * (D + 8) * sizeof(T) + (size_t)64 * (kBlock + 8) * sizeof(T);
     if (a.per_block_mean) {
         quant_rows_kernel<T, D, kModeQBlockMean><<<dim3(a.Nq_p / kBlock, BHq), 256, smem_q, st>>>(
-            q, a.qs[0], a.qs[1], a.qs[2], a.Hq, a.Nq, a.Nq_p, nullptr, qm, a.q_codes, a.q_sf, nullptr, nullptr, 0, 0);
+            q, a.qs[0], a.qs[1], a.qs[2], a.Hq, a.Nq, a.Nq_p, nullptr, qm, a.q_codes, a.q_sf);
     } else {
         // one mean per head over the padded rows (api.py:88-90); kpart is free again: the K finalize has
         // consumed it and stream order serializes the two uses
@@ -421,13 +481,13 @@ static cudaError_t launch_prepass_t(const PrepassArgs& a, cudaStream_t st) {
                                                                             a.kpart, a.kchunks_q);
         colmean_finalize_kernel<T, D><<<BHq, D, 0, st>>>(a.kpart, a.kchunks_q, 1.0f / (float)a.Nq_p, qm);
         quant_rows_kernel<T, D, kModeQGlobalMean><<<dim3(a.Nq_p / kBlock, BHq), 256, smem_q, st>>>(
-            q, a.qs[0], a.qs[1], a.qs[2], a.Hq, a.Nq, a.Nq_p, qm, nullptr, a.q_codes, a.q_sf, nullptr, nullptr, 0, 0);
+            q, a.qs[0], a.qs[1], a.qs[2], a.Hq, a.Nq, a.Nq_p, qm, nullptr, a.q_codes, a.q_sf);
     }
-    cudaError_t e = cudaFuncSetAttribute(quant_rows_kernel<T, D, kModeK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem_k);
+    const size_t smem_k = 2 * (D / 64) * 16384 + D * 4 + (D / 64) * 512 + 64 + 1024;
+    cudaError_t e = cudaFuncSetAttribute(quant_k_delta_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_k);
     if (e != cudaSuccess) return e;
-    quant_rows_kernel<T, D, kModeK><<<dim3(a.Nk_p / kBlock, BHkv), 256, smem_k, st>>>(
-        k, a.ks[0], a.ks[1], a.ks[2], a.Hkv, a.Nk, a.Nk_p, km, nullptr, a.k_codes, a.k_sf, qm, delta, a.Hq, a.nqm);
+    quant_k_delta_kernel<T, D><<<dim3(a.Nk_p / kBlock, BHkv), 256, smem_k, st>>>(
+        k, a.ks[0], a.ks[1], a.ks[2], a.Hkv, a.Nk, a.Nk_p, km, a.k_codes, a.k_sf, qm, delta, a.Hq, a.nqm, a.status);
 
     const size_t smem_v = ((kBlock * (D + 2) * sizeof(T) + 15) / 16) * 16 + D * 72 + 1024;
     e = cudaFuncSetAttribute(quant_vt_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_v);
