@@ -216,7 +216,7 @@ def main():
     import torch
     import torch.distributed as dist
     from oracle import sage3_oracle as O            # input generator + the cpu_baseline leg only
-    from sageattention_b200 import Sage3Problem, sageattn3
+    from sageattention_b200 import Sage3Problem, sageattn3_offload
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -317,9 +317,9 @@ def main():
         torch.cuda.synchronize()
 
         def e2e_step():
-            qd, kd, vd = (t_.to(dev, non_blocking=True) for t_ in (qh, kh, vh))
-            o = sageattn3(qd, kd, vd, tensor_layout=w["layout"], is_causal=w["causal"])
-            oh.copy_(o, non_blocking=True)
+            # the public call for host-resident operands: copies in, pre-pass, attention and copy out, pipelined
+            # over (batch, kv-head) chunks
+            sageattn3_offload(qh, kh, vh, out=oh, tensor_layout=w["layout"], is_causal=w["causal"], device=dev)
 
         e2e_step()
         torch.cuda.synchronize()

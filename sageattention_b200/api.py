@@ -186,3 +186,89 @@ def sageattn(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, retur
     """Signature of the reference's v2 dispatcher (core.py:79-88); on B200 it always runs the FP4 path."""
     return sageattn3(q, k, v, tensor_layout=tensor_layout, is_causal=is_causal, sm_scale=sm_scale,
                      return_lse=return_lse, **kwargs)
+
+
+def sageattn3_offload(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor | None = None,
+                      tensor_layout: str = "HND", is_causal: bool = False, sm_scale=None, per_block_mean: bool = True,
+                      device: torch.device | str | None = None, kv_heads_per_chunk: int | None = None) -> torch.Tensor:
+    """sageattn3 for operands that live in host memory (use pinned tensors): q, k, v are CPU tensors, the result
+    is a CPU tensor (pinned when allocated here).
+
+    (Batch, kv-head) groups are independent, so the call is pipelined over chunks of them on three streams:
+    while one chunk is being computed, the next one is copied in and the previous result is copied out.  Device
+    memory holds two chunks at a time, so the host tensors may be larger than the GPU.  The caller's current
+    stream orders the call as a whole (it is waited for at entry and waits for the last copy at exit; the host
+    is not blocked).  A scalar or None `sm_scale` only.
+    """
+    if any(t.is_cuda for t in (q, k, v)):
+        raise ValueError("sageattn3_offload takes host tensors; call sageattn3 for CUDA tensors")
+    if tensor_layout not in ("HND", "NHD"):
+        raise ValueError(f"tensor_layout must be 'HND' or 'NHD', got {tensor_layout!r}")
+    if isinstance(sm_scale, torch.Tensor):
+        raise ValueError("sageattn3_offload takes a scalar sm_scale")
+    dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    hd = 1 if tensor_layout == "HND" else 2
+    B, Hq, Hkv = q.shape[0], q.shape[hd], k.shape[hd]
+    if Hq % Hkv != 0:
+        raise ValueError(f"number of query heads ({Hq}) must be a multiple of kv heads ({Hkv})")
+    group = Hq // Hkv
+    if out is None:
+        out = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+    elif out.shape != q.shape or out.dtype != q.dtype or out.is_cuda:
+        raise ValueError("out must be a host tensor shaped and typed like q")
+    if kv_heads_per_chunk is None:
+        # about 16 chunks in total, whole kv heads per chunk
+        kv_heads_per_chunk = max(1, (B * Hkv + 15) // 16)
+    kv_heads_per_chunk = min(kv_heads_per_chunk, Hkv)
+    chunks = [(b, h0, min(h0 + kv_heads_per_chunk, Hkv)) for b in range(B) for h0 in range(0, Hkv, kv_heads_per_chunk)]
+
+    def cut(t, b, h0, h1, g=1):
+        return t[b:b + 1, h0 * g:h1 * g] if tensor_layout == "HND" else t[b:b + 1, :, h0 * g:h1 * g]
+
+    cur = torch.cuda.current_stream(dev)
+    s_in, s_comp, s_out = (torch.cuda.Stream(dev) for _ in range(3))
+    start = torch.cuda.Event()
+    start.record(cur)
+    for s_ in (s_in, s_comp, s_out):
+        s_.wait_event(start)
+    bufs = [None, None]          # per slot: (shape key, q_dev, k_dev, v_dev, problem)
+    comp_done = [None, None]
+    out_done = [None, None]
+    for i, (b, h0, h1) in enumerate(chunks):
+        slot = i & 1
+        qh, kh, vh = cut(q, b, h0, h1, group), cut(k, b, h0, h1), cut(v, b, h0, h1)
+        key = (tuple(qh.shape), tuple(kh.shape))
+        with torch.cuda.stream(s_in):
+            if comp_done[slot] is not None:
+                s_in.wait_event(comp_done[slot])            # the chunk that used these buffers has been computed
+            if bufs[slot] is None or bufs[slot][0] != key:
+                qd = torch.empty(qh.shape, dtype=q.dtype, device=dev)
+                kd = torch.empty(kh.shape, dtype=q.dtype, device=dev)
+                vd = torch.empty(vh.shape, dtype=q.dtype, device=dev)
+                prob = Sage3Problem(qd, kd, vd, tensor_layout, is_causal, sm_scale, per_block_mean)
+                for t_ in (qd, kd, vd, prob.out, prob.ws.buf):
+                    t_.record_stream(s_comp)
+                    t_.record_stream(s_out)
+                bufs[slot] = (key, qd, kd, vd, prob)
+            _, qd, kd, vd, prob = bufs[slot]
+            qd.copy_(qh, non_blocking=True)
+            kd.copy_(kh, non_blocking=True)
+            vd.copy_(vh, non_blocking=True)
+            in_done = torch.cuda.Event()
+            in_done.record(s_in)
+        with torch.cuda.stream(s_comp):
+            s_comp.wait_event(in_done)
+            if out_done[slot] is not None:
+                s_comp.wait_event(out_done[slot])           # the previous result in this slot has left the device
+            prob.run()
+            comp_done[slot] = torch.cuda.Event()
+            comp_done[slot].record(s_comp)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(comp_done[slot])
+            cut(out, b, h0, h1, group).copy_(prob.out, non_blocking=True)
+            out_done[slot] = torch.cuda.Event()
+            out_done[slot].record(s_out)
+    for ev in out_done:
+        if ev is not None:
+            cur.wait_event(ev)
+    return out

@@ -108,3 +108,18 @@ def test_bounded_wait_reports_instead_of_hanging(cuda_device):
     out = sageattn3(q, k, v)
     torch.cuda.synchronize()
     assert torch.isfinite(out.float()).all()
+
+
+@pytest.mark.parametrize("layout,causal", [("HND", False), ("NHD", True)])
+def test_offload_matches_device_call(cuda_device, layout, causal):
+    """Host-resident operands, pipelined over (batch, kv-head) chunks: same bits as the all-on-device call."""
+    from sageattention_b200 import sageattn3_offload
+    q, k, v = O.make_inputs(2, 8, 4, 300, 300, 64, seed=41, k_offset_std=1.0)
+    if layout == "NHD":
+        q, k, v = (t.transpose(1, 2).contiguous() for t in (q, k, v))
+    qp, kp, vp = (t.pin_memory() for t in (q, k, v))
+    ref = sageattn3(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), tensor_layout=layout, is_causal=causal).cpu()
+    for per_chunk in (1, 3, None):
+        out = sageattn3_offload(qp, kp, vp, tensor_layout=layout, is_causal=causal, kv_heads_per_chunk=per_chunk)
+        torch.cuda.synchronize()
+        assert torch.equal(out, ref), per_chunk
