@@ -164,8 +164,10 @@ def run_ulysses(args, w, q, k, v, flops, rank, world, local, dev):
     import torch.distributed as dist
     from sageattention_b200.ulysses import ulysses_attention
     stream = torch.cuda.current_stream()
+    hkv_l = w["Hkv"] // world
+    groups = max(1, min(args.overlap_groups if args.overlap_groups else 3, hkv_l))      # ulysses_attention's own rule
     for _ in range(max(args.warmup, 3)):
-        ulysses_attention(q, k, v, tensor_layout=w["layout"])
+        ulysses_attention(q, k, v, tensor_layout=w["layout"], overlap_groups=groups)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -174,7 +176,7 @@ def run_ulysses(args, w, q, k, v, flops, rank, world, local, dev):
     a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record(stream)
     for _ in range(args.steps):
-        ulysses_attention(q, k, v, tensor_layout=w["layout"])
+        ulysses_attention(q, k, v, tensor_layout=w["layout"], overlap_groups=groups)
     b_.record(stream)
     torch.cuda.synchronize()
     dist.barrier()
@@ -190,8 +192,9 @@ def run_ulysses(args, w, q, k, v, flops, rank, world, local, dev):
             vs_baseline=None, dtype="fp4 (e2m1 x ue4m3), fp32 accumulate", data="synthetic",
             config=dict(workload=args.workload, sharding="ulysses sequence parallel: NCCL all-to-all before and after attention",
                         tokens_per_rank=q.shape[2] if w["layout"] == "HND" else q.shape[1], heads_per_rank=w["Hq"] // world,
-                        all_to_all_bytes_per_rank_per_step=per_rank_bytes, l2="inputs larger than L2"),
-            clocks=clocks, gpu_launches=6 * args.steps)))
+                        all_to_all_bytes_per_rank_per_step=per_rank_bytes, head_slices_in_flight=groups,
+                        l2="inputs larger than L2"),
+            clocks=clocks, gpu_launches=6 * groups * args.steps)))
     dist.destroy_process_group()
 
 
@@ -207,6 +210,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ulysses", action="store_true",
                     help="strong scaling: the workload's tokens are sharded over the ranks (all-to-all before and after attention)")
+    ap.add_argument("--overlap-groups", type=int, default=0,
+                    help="with --ulysses: head slices whose all-to-all overlaps the kernels of the others (0 = up to 3)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     if args.impl == "reference":

@@ -75,7 +75,7 @@ def unpack_tokens_after_exchange(recv: torch.Tensor) -> torch.Tensor:
 # ------------------------------------------------------------------------------------------------------
 def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
                       is_causal: bool = False, group: dist.ProcessGroup | None = None,
-                      attn_fn: Callable | None = None, **kwargs) -> torch.Tensor:
+                      attn_fn: Callable | None = None, overlap_groups: int | None = None, **kwargs) -> torch.Tensor:
     """Sequence-parallel attention.  Every rank passes its contiguous token shard
     [rank * N/P, (rank + 1) * N/P) of all heads and gets the output for the same shard.
 
@@ -83,6 +83,10 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_
     multiples of the group size.  `attn_fn(q, k, v, tensor_layout="HND", is_causal=..., **kwargs)` defaults to
     sageattn3; the result equals attn_fn on the gathered tensors, bit for bit, because every head is
     computed by exactly one rank from exactly the same inputs.
+
+    The rank's heads are processed in `overlap_groups` slices (default: up to 3, whole kv heads each): the
+    all-to-all of slice g + 1 and the return all-to-all of slice g - 1 run on NCCL's stream while slice g is
+    in the pre-pass and attention kernels.
     """
     if attn_fn is None:
         from .api import sageattn3 as attn_fn
@@ -90,15 +94,37 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_
     qh, kh, vh = (_to_hnd(t, tensor_layout) for t in (q, k, v))
     if world == 1:
         o = attn_fn(qh.contiguous(), kh.contiguous(), vh.contiguous(), tensor_layout="HND", is_causal=is_causal, **kwargs)
-    else:
-        Hq, Hkv = qh.shape[1], kh.shape[1]
-        send = pack_heads_for_exchange(qh, kh, vh, world)
+        return o if tensor_layout == "HND" else o.transpose(1, 2)
+    B, Hq, n, D = qh.shape
+    Hkv = kh.shape[1]
+    if Hq % world or Hkv % world:
+        raise ValueError(f"Ulysses needs the head counts ({Hq}, {Hkv}) to be multiples of the world size {world}")
+    hq_l, hkv_l = Hq // world, Hkv // world          # heads this rank computes
+    rep = hq_l // hkv_l
+    G = overlap_groups if overlap_groups is not None else min(3, hkv_l)
+    G = max(1, min(G, hkv_l))
+    bounds = [(g * hkv_l) // G for g in range(G + 1)]      # slices of the local kv heads
+    q5, k5, v5 = (t.reshape(B, world, -1, n, D) for t in (qh, kh, vh))   # [B, dest rank, its heads, n, D]
+    works_in, recvs = [], []
+    for g in range(G):
+        a, b_ = bounds[g], bounds[g + 1]
+        send = pack_heads_for_exchange(q5[:, :, a * rep:b_ * rep].reshape(B, -1, n, D), k5[:, :, a:b_].reshape(B, -1, n, D),
+                                       v5[:, :, a:b_].reshape(B, -1, n, D), world)
         recv = torch.empty_like(send)
-        dist.all_to_all_single(recv, send, group=group)
-        ql, kl, vl = unpack_heads_after_exchange(recv, Hq // world, Hkv // world)
+        works_in.append(dist.all_to_all_single(recv, send, group=group, async_op=True))
+        recvs.append((recv, send))
+    out5 = torch.empty(B, world, hq_l, n, D, dtype=qh.dtype, device=qh.device)
+    works_out = []
+    for g in range(G):
+        a, b_ = bounds[g], bounds[g + 1]
+        works_in[g].wait()
+        ql, kl, vl = unpack_heads_after_exchange(recvs[g][0], (b_ - a) * rep, b_ - a)
         ol = attn_fn(ql.contiguous(), kl.contiguous(), vl.contiguous(), tensor_layout="HND", is_causal=is_causal, **kwargs)
         send_o = pack_tokens_for_exchange(ol, world)
         recv_o = torch.empty_like(send_o)
-        dist.all_to_all_single(recv_o, send_o, group=group)
-        o = unpack_tokens_after_exchange(recv_o)
+        works_out.append((dist.all_to_all_single(recv_o, send_o, group=group, async_op=True), recv_o, send_o, a, b_))
+    for work, recv_o, _send_o, a, b_ in works_out:
+        work.wait()
+        out5[:, :, a * rep:b_ * rep] = recv_o.permute(1, 0, 2, 3, 4)     # [B, source rank, its slice of heads, n, D]
+    o = out5.reshape(B, Hq, n, D)
     return o if tensor_layout == "HND" else o.transpose(1, 2)

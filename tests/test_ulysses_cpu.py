@@ -87,3 +87,27 @@ def test_two_ranks_over_gloo_match_single_process(layout):
         ret = mgr.dict()
         mp.spawn(_worker, args=(world, _free_port(), layout, ret), nprocs=world, join=True)
         assert dict(ret) == {0: True, 1: True}
+
+
+def _worker_slices(rank, world, port, groups, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        q, k, v = O.make_inputs(1, 12, 6, 128, 128, 64, seed=78, k_offset_std=1.0)
+        n = 128 // world
+        cut = lambda x: x[:, :, rank * n:(rank + 1) * n]
+        out = U.ulysses_attention(cut(q), cut(k), cut(v), attn_fn=O.sageattn3_oracle, overlap_groups=groups)
+        full = O.sageattn3_oracle(q, k, v)
+        ret[rank] = bool(torch.equal(out, cut(full)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("groups", [None, 2, 7])
+def test_head_slices_overlap_gives_the_same_result(groups):
+    """Three kv heads (six q heads) per rank, processed in 3, 2 (uneven) and 3 (clamped) slices."""
+    world = 2
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker_slices, args=(world, _free_port(), groups, ret), nprocs=world, join=True)
+        assert dict(ret) == {0: True, 1: True}
