@@ -1,18 +1,20 @@
 // Block-scaled FP4 attention for sm_100a: TMA-staged E2M1 tiles, tcgen05 NVFP4 MMAs with the S and O
 // accumulators in tensor memory, exp2 online softmax, P re-quantized to NVFP4 before the PV MMA.
 //
-// One CTA per 128-row query tile.  Four warpgroups (setmaxnreg moves registers to the exp warpgroups):
-//   warp 0       TMA producer (one lane): Q once, then K (+ delta_s row) / V^T / scale atoms per KV block
+// One CTA per PAIR of 128-row query tiles of one head; every K / V^T stage in shared memory serves both
+// tiles.  Three warpgroups (setmaxnreg moves registers to the softmax warpgroups):
+//   warp 0       TMA producer (one lane): both Q tiles once, then K (+ one delta_s row per tile) / V^T /
+//                scale atoms per KV block
 //   warp 1       Q K^T MMA issuer (one lane) and owner of the tensor-memory allocation
 //   warp 2       P V MMA issuer (one lane); warp 3 idle
-//   warps 4-11   exp: two warpgroups that take alternate KV blocks; thread = row with all 128 scores of the block
-//                in registers -> exp2 values, their row sum and FP4 codes of P; bound by the exp2 unit
-//   warps 12-15  stats + correction: thread = row; one block ahead of the exp warps it reads the whole S row,
-//                derives microblock maxima, running maximum, rescale factor and per-microblock constants
-//                (shared memory -> exp warps), rescales O in tensor memory when a row maximum moved, and
-//                finally writes O / l to global memory
-// S is double-buffered in tensor memory so that Q K^T and the statistics of block j+1 overlap the exp2 work
-// of block j.
+//   warps 4-7    softmax of query tile 0, warps 8-11 softmax of query tile 1: thread = row.  Per KV block the
+//                thread pulls its 128 scores out of tensor memory into registers (which frees the S buffer
+//                for the other tile at once), finds the microblock maxima and the running maximum, forms
+//                exp2 values, their row sum and the FP4 codes + E4M3 scales of P, rescales its own O row in
+//                tensor memory when the maximum moved, and finally writes O / l
+// The two softmax warpgroups own different query tiles, so neither ever waits for a value of the other: their
+// only shared resources are the single S buffer (held for one MMA + one load), the MMA issuers and the exp2
+// unit, which one warpgroup keeps busy while the other is in its load / maximum / store phases.
 //
 // Arithmetic follows (paths inside the reference project, sageattention3_blackwell/sageattn3/blackwell/...):
 //   mainloop_tma_ws.h:509, 532-551, 865     KV blocks are walked from the last to the first
@@ -33,15 +35,10 @@
 
 namespace sage3 {
 
-// Optional per-phase cycle accounting of the first CTA (development builds only; off in the product library).
 #ifdef SAGE3_PHASE_TIMING
-#define PT_DECL long long pt_t = clock64(); long long pt_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#define PT(i) { const long long pt_now = clock64(); pt_acc[i] += pt_now - pt_t; pt_t = pt_now; }
-#define PT_DUMP(slot) if (p.debug != nullptr && blockIdx.x == 0 && lane == 0) { for (int i_ = 0; i_ < 8; ++i_) p.debug[40000 + (slot) * 8 + i_] = (float)pt_acc[i_]; }
+#define TS(slot, cond) if (p.debug != nullptr && blockIdx.x == 0 && (cond)) p.debug[40000 + (slot)] = (float)(clock64() - *reinterpret_cast<volatile long long*>(sgen + C::oMisc + 16));
 #else
-#define PT_DECL
-#define PT(i)
-#define PT_DUMP(slot)
+#define TS(slot, cond)
 #endif
 
 constexpr float kLog2Of6 = 2.584962500721156f;
@@ -56,41 +53,38 @@ struct AttnParams {
     void* out;
     int64_t os0, os1, os2;
     int* status;
-    float* debug;                       // optional dump of CTA 0 (nullptr in normal use)
+    float* debug;                       // optional dump of CTA 0, tile 0 (nullptr in normal use)
 };
 
 template <int D>
 struct Cfg {
-    static constexpr int kStages = (D == 128) ? 6 : 8;
-    static constexpr int kThreads = 512;                      // 4 warpgroups, see the kernel
-    static constexpr int kQBytes = 128 * D / 2;
+    static constexpr int kStages = 6;                         // K and V^T stages, each shared by the two query tiles
+    static constexpr int kThreads = 384;                      // 3 warpgroups, see the kernel
+    static constexpr int kQBytes = 128 * D / 2;               // per query tile
     static constexpr int kSfQkBytes = (D / 64) * 512;
     static constexpr int kKBytes = 128 * D / 2;
     static constexpr int kVBytes = D * 64;
     static constexpr int kSfVBytes = 1024;
     static constexpr int kDeltaBytes = 256;
     static constexpr int kPBytes = 8192;
-    static constexpr int kSfPBytes = 1024;
     // shared-memory map (bytes from a 1024-aligned base)
-    static constexpr int oQ = 0;
-    static constexpr int oK = oQ + 8192;
+    static constexpr int oQ = 0;                              // [tile] 8192
+    static constexpr int oK = oQ + 2 * 8192;
     static constexpr int oV = oK + kStages * 8192;
-    static constexpr int oP = oV + kStages * 8192;
-    static constexpr int oSfQ = oP + 2 * kPBytes;
-    static constexpr int oSfK = oSfQ + 1024;
+    static constexpr int oP = oV + kStages * 8192;            // [tile][buffer] 8192
+    static constexpr int oSfQ = oP + 4 * kPBytes;             // [tile] 1024
+    static constexpr int oSfK = oSfQ + 2 * 1024;
     static constexpr int oSfV = oSfK + kStages * 1024;
-    static constexpr int oSfP = oSfV + kStages * 1024;
-    static constexpr int oDelta = oSfP + 2 * 1024;
+    static constexpr int oSfP = oSfV + kStages * 1024;        // [tile][buffer] 1024
     static constexpr int kDeltaPitch = 512;                   // 256 B of delta_s + 256 B that stay zero
-    static constexpr int oOnes = oDelta + kStages * kDeltaPitch;   // 128 x 16 tile: column 0 = 1.0, rest 0
-    static constexpr int oCst = oOnes + 4096;                 // float [2][17][128]  per block: 8 offsets, 8 scales, scaled max per row
-    static constexpr int oL = oCst + 2 * 17 * 128 * 4;        // float [2][2][128]   per exp warpgroup: row sum, scaled max it refers to
-    static constexpr int oBar = oL + 4 * 128 * 4;
-    static constexpr int kNumBars = 1 + 4 * kStages + 2 + 2 + 1 + 2 + 1;
+    static constexpr int oDelta = oSfP + 4 * 1024;            // [stage][tile] kDeltaPitch
+    static constexpr int oOnes = oDelta + kStages * 2 * kDeltaPitch;   // 128 x 16 tile: column 0 = 1.0, rest 0
+    static constexpr int oBar = oOnes + 4096;
+    static constexpr int kNumBars = 1 + 4 * kStages + 2 + 1 + 4 + 4;
     static constexpr int oMisc = oBar + kNumBars * 8;
     static constexpr int kSmemBytes = oMisc + 64 + 1024;      // + slack for the manual 1024-byte alignment
-    // tensor-memory columns
-    static constexpr uint32_t cS0 = 0, cS1 = 128, cO = 256, cSfQ = 384, cSfK = 392, cSfP = 400, cSfV = 408;
+    // tensor-memory columns: one S buffer, one O accumulator per tile, scale factors
+    static constexpr uint32_t cS = 0, cO = 128, cSfQ = 384, cSfK = 400, cSfV = 408, cSfP = 416;
     static constexpr uint64_t kSwzQK = (D == 128) ? kSwz64 : kSwz32;
     static constexpr uint32_t kSboQK = (D == 128) ? 512 : 256;
 };
@@ -140,49 +134,62 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
     // barriers
     auto bar = [&](int i) { return sbase + C::oBar + 8u * i; };
-    const int bQ = 0, bKF = 1, bQK = bKF + S, bVF = bQK + S, bPV = bVF + S, bSE = bPV + S, bPF = bSE + 2,
-              bOS = bPF + 2, bST = bOS + 1, bLR = bST + 2;
+    const int bQ = 0, bKF = 1, bKE = bKF + S, bVF = bKE + S, bVE = bVF + S, bSF = bVE + S, bSE = bSF + 2,
+              bPF = bSE + 1, bPV = bPF + 4;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + C::oMisc);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + C::oMisc + 8);
 
-    // tile -> (batch*head, query tile); heavier causal tiles are scheduled first
-    const int bhq = blockIdx.x / p.nqt;
-    int mt = blockIdx.x % p.nqt;
-    if (CAUSAL) mt = p.nqt - 1 - mt;
+    // CTA -> (batch*head, pair of query tiles); heavier causal pairs are scheduled first
+    const int npair = (p.nqt + 1) >> 1;
+    const int bhq = blockIdx.x / npair;
+    int pr = blockIdx.x % npair;
+    if (CAUSAL) pr = npair - 1 - pr;
+    const int mt0 = 2 * pr;
+    const int nv = (mt0 + 1 < p.nqt) ? 2 : 1;            // query tiles this CTA really has
     const int b = bhq / p.Hq, hq = bhq % p.Hq;
     const int bhkv = b * p.Hkv + hq / (p.Hq / p.Hkv);
     const int shift = p.Nk - p.Nq;
-    int nb = p.nkb;
-    if (CAUSAL) {
-        const int max_key = min(p.Nk - 1, mt * kBlock + kBlock - 1 + shift);
-        nb = max_key < 0 ? 0 : max_key / kBlock + 1;
-    }
     const bool dead_launch = (*reinterpret_cast<volatile int*>(p.status) != 0);   // an earlier CTA gave up
-    if (dead_launch) nb = 0;
+    // KV blocks of tile t: [0, nbt[t]); the CTA walks block n = nbmax - 1 ... 0 and tile t joins at step skip[t]
+    int nbt[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        int nb = p.nkb;
+        if (CAUSAL) {
+            const int max_key = min(p.Nk - 1, (mt0 + t) * kBlock + kBlock - 1 + shift);
+            nb = max_key < 0 ? 0 : max_key / kBlock + 1;
+        }
+        nbt[t] = (dead_launch || t >= nv) ? 0 : nb;
+    }
+    const int nbmax = max(nbt[0], nbt[1]);
+    const int skip[2] = {nbmax - nbt[0], nbmax - nbt[1]};
 
+#ifdef SAGE3_PHASE_TIMING
+    if (threadIdx.x == 0) *reinterpret_cast<volatile long long*>(sgen + C::oMisc + 16) = clock64();
+#endif
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         mbar_init(bar(bQ), 1);
         for (int i = 0; i < S; ++i) {
             mbar_init(bar(bKF + i), 1);
-            mbar_init(bar(bQK + i), 1);    // Q K^T (+ delta_s) of the block in stage i is complete: its S buffer is full, the K stage is free
+            mbar_init(bar(bKE + i), 1);    // every Q K^T that reads K stage i is complete
             mbar_init(bar(bVF + i), 1);
-            mbar_init(bar(bPV + i), 1);    // P V of the block in stage i is complete: O is up to date, V stage and P buffer are free
+            mbar_init(bar(bVE + i), 1);    // every P V that reads V stage i is complete
         }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(bar(bSE + i), 8);    // the exp warpgroup of the block (4 warps) and the stats warps (4) have read S buffer i
-            mbar_init(bar(bST + i), 4);    // constants of the block in S buffer i are in shared memory  (stats warps)
-            mbar_init(bar(bPF + i), 4);    // P buffer i (+ its scales) is written
+        mbar_init(bar(bSF), 1);            // S holds the scores of tile 0's next block
+        mbar_init(bar(bSF + 1), 1);        // ... of tile 1's next block
+        mbar_init(bar(bSE), 4);            // the four warps of the tile that owns S have it in registers
+        for (int i = 0; i < 4; ++i) {
+            mbar_init(bar(bPF + i), 4);    // [tile][buffer]: P (+ scales) written and O rescaled
+            mbar_init(bar(bPV + i), 1);    // [tile][buffer]: the P V MMA that read it is complete
         }
-        mbar_init(bar(bOS), 4);            // O has been rescaled for the next PV          (stats warps)
-        mbar_init(bar(bLR), 8);            // final row sums of both exp warpgroups are in shared memory
         mbar_fence_init();
     }
     {
         // delta_s stages: the 256 bytes behind each row stay zero for the whole kernel; ones tile:
         // [k chunk][row group][8 rows][16 bytes], 1.0 in element 0 of every row of chunk 0
         uint4* z = reinterpret_cast<uint4*>(sgen + C::oDelta);
-        for (int i = threadIdx.x; i < (S * C::kDeltaPitch + 4096) / 16; i += blockDim.x) z[i] = make_uint4(0, 0, 0, 0);
+        for (int i = threadIdx.x; i < (S * 2 * C::kDeltaPitch + 4096) / 16; i += blockDim.x) z[i] = make_uint4(0, 0, 0, 0);
         __syncthreads();
         if (threadIdx.x < 128) {
             const uint16_t one = std::is_same<OutT, __nv_bfloat16>::value ? 0x3F80 : 0x3C00;
@@ -205,30 +212,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t tmem = *tmem_slot;
 
     const float sl2 = p.sm_scale_per_head ? p.sm_scale_per_head[hq] * 1.4426950408889634f : p.sm_scale_log2;
-    float* s_cst = reinterpret_cast<float*>(sgen + C::oCst);
-    float* s_l = reinterpret_cast<float*>(sgen + C::oL);
 
-    // Register budget: 512 threads start with 128 registers each; the exp warpgroups (a whole S row per thread)
-    // take what warpgroup 0 (two single-lane roles) and the stats warpgroup do not need.
+    // Register budget: 384 threads start with 168 registers each; the softmax warpgroups (a whole S row per
+    // thread) take what warpgroup 0 (three single-lane roles) does not need.
     if (warp < 4) {
       reg_dealloc<48>();
       if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
-        if (lane == 0 && nb > 0) {
-            mbar_expect_tx(bar(bQ), C::kQBytes + C::kSfQkBytes);
-            tma_load_3d(sbase + C::oQ, &tm_q, bar(bQ), 0, mt * kBlock, bhq);
-            bulk_load(sbase + C::oSfQ, p.q_sf + ((size_t)bhq * p.nqt + mt) * C::kSfQkBytes, C::kSfQkBytes, bar(bQ));
-            const int drow = (p.nqm > 1) ? mt : 0;
-            const uint16_t* dptr = p.delta + ((size_t)bhq * p.nqm + drow) * ((size_t)p.nkb * kBlock);
-            for (int j = 0; j < nb; ++j) {
-                const int n = nb - 1 - j, st = j % S;
-                if (j >= S && !mbar_wait<true>(bar(bQK + st), ((j / S) - 1) & 1, abort_flag, p.status, kWaitKEmpty)) break;
-                mbar_expect_tx(bar(bKF + st), C::kKBytes + C::kSfQkBytes + C::kDeltaBytes);
+        if (lane == 0 && nbmax > 0) {
+            mbar_expect_tx(bar(bQ), nv * (C::kQBytes + C::kSfQkBytes));
+            const uint16_t* dptr[2];
+            for (int t = 0; t < nv; ++t) {
+                tma_load_3d(sbase + C::oQ + t * 8192, &tm_q, bar(bQ), 0, (mt0 + t) * kBlock, bhq);
+                bulk_load(sbase + C::oSfQ + t * 1024, p.q_sf + ((size_t)bhq * p.nqt + mt0 + t) * C::kSfQkBytes,
+                          C::kSfQkBytes, bar(bQ));
+                const int drow = (p.nqm > 1) ? mt0 + t : 0;
+                dptr[t] = p.delta + ((size_t)bhq * p.nqm + drow) * ((size_t)p.nkb * kBlock);
+            }
+            for (int jj = 0; jj < nbmax; ++jj) {
+                const int n = nbmax - 1 - jj, st = jj % S;
+                if (jj >= S && !mbar_wait<true>(bar(bKE + st), ((jj / S) - 1) & 1, abort_flag, p.status, kWaitKEmpty)) break;
+                mbar_expect_tx(bar(bKF + st), C::kKBytes + C::kSfQkBytes + nv * C::kDeltaBytes);
                 tma_load_3d(sbase + C::oK + st * 8192, &tm_k, bar(bKF + st), 0, n * kBlock, bhkv);
                 bulk_load(sbase + C::oSfK + st * 1024, p.k_sf + ((size_t)bhkv * p.nkb + n) * C::kSfQkBytes,
                           C::kSfQkBytes, bar(bKF + st));
-                bulk_load(sbase + C::oDelta + st * C::kDeltaPitch, dptr + (size_t)n * kBlock, C::kDeltaBytes, bar(bKF + st));
-                if (j >= S && !mbar_wait<true>(bar(bPV + st), ((j / S) - 1) & 1, abort_flag, p.status, kWaitVEmpty)) break;
+                for (int t = 0; t < nv; ++t)
+                    bulk_load(sbase + C::oDelta + (st * 2 + t) * C::kDeltaPitch, dptr[t] + (size_t)n * kBlock,
+                              C::kDeltaBytes, bar(bKF + st));
+                if (jj >= S && !mbar_wait<true>(bar(bVE + st), ((jj / S) - 1) & 1, abort_flag, p.status, kWaitVEmpty)) break;
                 mbar_expect_tx(bar(bVF + st), C::kVBytes + C::kSfVBytes);
                 tma_load_3d(sbase + C::oV + st * 8192, &tm_v, bar(bVF + st), n * 64, 0, bhkv);
                 bulk_load(sbase + C::oSfV + st * 1024, p.v_sf + ((size_t)bhkv * p.nkb + n) * C::kSfVBytes,
@@ -238,119 +249,122 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         __syncwarp();
       } else if (warp == 1) {
         // ------------------------------------------------------------------ Q K^T MMA issuer
-        if (lane == 0 && nb > 0) {
+        // The single S buffer is handed from tile to tile: it is free again as soon as the four warps of the
+        // tile that owned it hold the scores in registers.
+        if (lane == 0 && nbmax > 0) {
             constexpr uint32_t idesc_qk = make_idesc_nvfp4(128);
             constexpr uint32_t idesc_delta = make_idesc_f16_bmn(128, std::is_same<OutT, __nv_bfloat16>::value);
-            const uint64_t q_desc = make_sdesc(sbase + C::oQ, 16, C::kSboQK, C::kSwzQK);
             const uint64_t ones_desc = make_sdesc(sbase + C::oOnes, 2048, 128, kSwzNone);
-            auto issue_qk = [&](int j) -> bool {
-                const int st = j % S, bb = j & 1;
-                if (j >= 2 && !mbar_wait(bar(bSE + bb), ((j >> 1) - 1) & 1, abort_flag, p.status, kWaitSEmpty)) return false;
-                if (!mbar_wait(bar(bKF + st), (j / S) & 1, abort_flag, p.status, kWaitKFull)) return false;
+            bool ok = mbar_wait(bar(bQ), 0, abort_flag, p.status, kWaitQFull);
+            if (ok) {
+                for (int t = 0; t < nv; ++t)
+#pragma unroll
+                    for (int ks = 0; ks < D / 64; ++ks)
+                        tc_cp_sf(tmem + C::cSfQ + 8 * t + 4 * ks, make_sdesc(sbase + C::oSfQ + t * 1024 + ks * 512, 0, 128, kSwzNone));
+            }
+            int uses = 0;
+            for (int jj = 0; ok && jj < nbmax; ++jj) {
+                const int st = jj % S;
+                TS(0, jj == 20)
+                if (!mbar_wait(bar(bKF + st), (jj / S) & 1, abort_flag, p.status, kWaitKFull)) { ok = false; break; }
+                TS(1, jj == 20)
                 tc_fence_after();
                 const uint64_t k_desc = make_sdesc(sbase + C::oK + st * 8192, 16, C::kSboQK, C::kSwzQK);
 #pragma unroll
                 for (int ks = 0; ks < D / 64; ++ks)
                     tc_cp_sf(tmem + C::cSfK + 4 * ks, make_sdesc(sbase + C::oSfK + st * 1024 + ks * 512, 0, 128, kSwzNone));
-                // S <- 1 (x) delta_s: A = [128 x 16] with ones in column 0 (K-major), B = the delta_s row read as an
-                // MN-major [16 x 128] operand whose rows 1..15 alias finite data and meet zeros in A
-                tc_mma_f16(tmem + (bb ? C::cS1 : C::cS0), ones_desc,
-                           make_sdesc(sbase + C::oDelta + st * C::kDeltaPitch, 16, 16, kSwzNone), idesc_delta, false);
+                for (int t = 0; t < 2; ++t) {
+                    if (jj < skip[t]) continue;
+                    TS(2 + 4 * t, jj == 20)
+                    if (uses > 0 && !mbar_wait(bar(bSE), (uses - 1) & 1, abort_flag, p.status, kWaitSEmpty)) { ok = false; break; }
+                    TS(3 + 4 * t, jj == 20)
+                    tc_fence_after();
+                    const uint64_t q_desc = make_sdesc(sbase + C::oQ + t * 8192, 16, C::kSboQK, C::kSwzQK);
+                    // S <- 1 (x) delta_s: A = [128 x 16] with ones in column 0 (K-major), B = the delta_s row read as an
+                    // MN-major [16 x 128] operand whose rows 1..15 alias finite data and meet zeros in A
+                    tc_mma_f16(tmem + C::cS, ones_desc,
+                               make_sdesc(sbase + C::oDelta + (st * 2 + t) * C::kDeltaPitch, 16, 16, kSwzNone), idesc_delta, false);
 #pragma unroll
-                for (int ks = 0; ks < D / 64; ++ks)
-                    tc_mma_nvfp4(tmem + (bb ? C::cS1 : C::cS0), q_desc + 2 * ks, k_desc + 2 * ks, idesc_qk,
-                                 tmem + C::cSfQ + 4 * ks, tmem + C::cSfK + 4 * ks, true);
-                tc_commit(bar(bQK + st));
-                return true;
-            };
-            PT_DECL
-            bool ok = mbar_wait(bar(bQ), 0, abort_flag, p.status, kWaitQFull);
-            if (ok) {
-#pragma unroll
-                for (int ks = 0; ks < D / 64; ++ks)
-                    tc_cp_sf(tmem + C::cSfQ + 4 * ks, make_sdesc(sbase + C::oSfQ + ks * 512, 0, 128, kSwzNone));
+                    for (int ks = 0; ks < D / 64; ++ks)
+                        tc_mma_nvfp4(tmem + C::cS, q_desc + 2 * ks, k_desc + 2 * ks, idesc_qk,
+                                     tmem + C::cSfQ + 8 * t + 4 * ks, tmem + C::cSfK + 4 * ks, true);
+                    TS(4 + 4 * t, jj == 20)
+                    tc_commit(bar(bSF + t));
+                    TS(5 + 4 * t, jj == 20)
+                    ++uses;
+                }
+                if (ok) tc_commit(bar(bKE + st));
             }
-            // S buffer j & 1 is free as soon as block j - 2 sits in the registers of its exp and stats warps
-            for (int j = 0; ok && j < nb; ++j) {
-                ok = issue_qk(j);
-                PT(0)
-            }
-            PT_DUMP(1)
         }
         __syncwarp();
       } else if (warp == 2) {
         // ------------------------------------------------------------------ PV MMA issuer
-        if (lane == 0 && nb > 0) {
+        if (lane == 0 && nbmax > 0) {
             constexpr uint32_t idesc_pv = make_idesc_nvfp4(D);
-            PT_DECL
-            for (int j = 0; j < nb; ++j) {
-                const int st = j % S, bb = j & 1;
-                if (!mbar_wait(bar(bVF + st), (j / S) & 1, abort_flag, p.status, kWaitVFull)) break;
-                PT(1)
-                if (!mbar_wait(bar(bPF + bb), (j >> 1) & 1, abort_flag, p.status, kWaitPFull)) break;
-                PT(2)
-                if (!mbar_wait(bar(bOS), j & 1, abort_flag, p.status, kWaitOScaled)) break;
-                PT(3)
-                tc_fence_after();
-                const uint64_t p_desc = make_sdesc(sbase + C::oP + bb * C::kPBytes, 16, 512, kSwz64);
+            bool ok = true;
+            for (int jj = 0; ok && jj < nbmax; ++jj) {
+                const int st = jj % S;
+                if (!mbar_wait(bar(bVF + st), (jj / S) & 1, abort_flag, p.status, kWaitVFull)) break;
                 const uint64_t v_desc = make_sdesc(sbase + C::oV + st * 8192, 16, 512, kSwz64);
+                bool first = true;
+                for (int t = 0; t < 2; ++t) {
+                    if (jj < skip[t]) continue;
+                    const int j = jj - skip[t], pb = t * 2 + (j & 1);
+                    if (!mbar_wait(bar(bPF + pb), (j >> 1) & 1, abort_flag, p.status, kWaitPFull)) { ok = false; break; }
+                    tc_fence_after();
+                    if (first) {
 #pragma unroll
-                for (int ks = 0; ks < 2; ++ks) {
-                    tc_cp_sf(tmem + C::cSfP + 4 * ks, make_sdesc(sbase + C::oSfP + bb * 1024 + ks * 512, 0, 128, kSwzNone));
-                    tc_cp_sf(tmem + C::cSfV + 4 * ks, make_sdesc(sbase + C::oSfV + st * 1024 + ks * 512, 0, 128, kSwzNone));
+                        for (int ks = 0; ks < 2; ++ks)
+                            tc_cp_sf(tmem + C::cSfV + 4 * ks, make_sdesc(sbase + C::oSfV + st * 1024 + ks * 512, 0, 128, kSwzNone));
+                        first = false;
+                    }
+                    const uint64_t p_desc = make_sdesc(sbase + C::oP + pb * C::kPBytes, 16, 512, kSwz64);
+#pragma unroll
+                    for (int ks = 0; ks < 2; ++ks)
+                        tc_cp_sf(tmem + C::cSfP + 4 * ks, make_sdesc(sbase + C::oSfP + pb * 1024 + ks * 512, 0, 128, kSwzNone));
+#pragma unroll
+                    for (int ks = 0; ks < 2; ++ks)
+                        tc_mma_nvfp4(tmem + C::cO + t * 128, p_desc + 2 * ks, v_desc + 2 * ks, idesc_pv, tmem + C::cSfP + 4 * ks,
+                                     tmem + C::cSfV + 4 * ks, (j > 0) || (ks > 0));
+                    tc_commit(bar(bPV + pb));
                 }
-#pragma unroll
-                for (int ks = 0; ks < 2; ++ks)
-                    tc_mma_nvfp4(tmem + C::cO, p_desc + 2 * ks, v_desc + 2 * ks, idesc_pv, tmem + C::cSfP + 4 * ks,
-                                 tmem + C::cSfV + 4 * ks, (j > 0) || (ks > 0));
-                tc_commit(bar(bPV + st));
-                PT(4)
+                if (ok) tc_commit(bar(bVE + st));
             }
-            PT_DUMP(2)
         }
         __syncwarp();
       }   // warp 3: no role (it completes warpgroup 0 so that it can give its registers away)
-    } else if (warp < 12) {
-        reg_alloc<184>();
-        // ------------------------------------------------------------------ exp warpgroups (2 x 4 warps)
-        // Warpgroup `par` handles the blocks j = par, par + 2, ...; thread = row r with all 128 scores of the
-        // block in registers.  The block's constants (per-microblock offsets and scales, scaled running
-        // maximum) come from the stats warps through shared memory; their arrival also tells that S(j) is
-        // complete.  The two warpgroups are never
-        // synchronised with each other: the loads, waits and stores of one overlap the exp2 work of the other.
+    } else {
+        reg_alloc<224>();
+        // ------------------------------------------------------------------ softmax warpgroups (2 x 4 warps)
+        // Warpgroup t owns query tile t: thread = row r, with the row's running maximum, row sum and O row.
+        const int t = (warp >> 2) - 1;
         const int quarter = warp & 3;            // tensor-memory lane quarter this warp may touch
-        const int par = (warp >> 2) - 1;         // block parity; also the S buffer and the P buffer it uses
         const int r = quarter * 32 + lane;       // row inside the tile
         const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+        const int mt = mt0 + t;
+        const int nb = nbt[t];
         const int grow = mt * kBlock + r;        // query index
-        const uint32_t s_addr = tmem + lane_addr + (par ? C::cS1 : C::cS0);
-        const float* cst = s_cst + par * (17 * 128) + r;
-        uint8_t* prow = sgen + C::oP + par * C::kPBytes + r * 64;
-        uint32_t* sfp_row = reinterpret_cast<uint32_t*>(sgen + C::oSfP + par * 1024 + (r & 31) * 16 + (r >> 5) * 4);
+        const uint32_t s_addr = tmem + lane_addr + C::cS;
+        const uint32_t o_addr = tmem + lane_addr + C::cO + t * 128;
         const int sw = (r >> 1) & 3;
         const uint64_t sl2x2 = pack2f(sl2, sl2);
-        float l_run = 0.f, ms_prev = -INFINITY;
+        const bool dbg = (p.debug != nullptr && blockIdx.x == 0 && t == 0);
+        float m_run = -INFINITY, l_run = 0.f;
         bool alive = true;
-        PT_DECL
-        for (int j = par; j < nb; j += 2) {
-            const int n = nb - 1 - j;
-            if (!warp_wait(bar(bST + par), (j >> 1) & 1, abort_flag, p.status, kWaitStats)) { alive = false; break; }
+        for (int j = 0; j < nb; ++j) {
+            const int n = nb - 1 - j, pb = t * 2 + (j & 1);
+            TS(16 + 8 * t + 0, j == 20 && quarter == 0 && lane == 0)
+            if (!warp_wait(bar(bSF + t), j & 1, abort_flag, p.status, kWaitSFull)) { alive = false; break; }
+            TS(16 + 8 * t + 1, j == 20 && quarter == 0 && lane == 0)
             tc_fence_after();
             float s[128];
 #pragma unroll
             for (int c4 = 0; c4 < 4; ++c4) tmem_ld32(s_addr + c4 * 32, s + c4 * 32);
-            float negc[8], sfv[8];
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                negc[g] = cst[g * 128];
-                sfv[g] = cst[(8 + g) * 128];
-            }
-            const float ms = cst[16 * 128];
             tc_wait_ld();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(bSE + par));     // S(j) is in registers, its constants are read
-            PT(4)
+            if (lane == 0) mbar_arrive(bar(bSE));     // S is in registers: the other tile's Q K^T may overwrite it
+            TS(16 + 8 * t + 2 + quarter, j == 20 && lane == 0)
             const bool need_mask = ((n + 1) * kBlock > p.Nk) || (CAUSAL && (n * kBlock + kBlock - 1 > mt * kBlock + shift));
             if (need_mask) {
                 int lim = p.Nk - 1;
@@ -360,16 +374,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 for (int i = 0; i < 128; ++i)
                     if (key0 + i > lim) s[i] = -INFINITY;
             }
-            if (p.debug != nullptr && blockIdx.x == 0 && j == 0) {
+            if (dbg && j == 0) {
 #pragma unroll
                 for (int i = 0; i < 128; ++i) p.debug[r * 128 + i] = s[i];
             }
+            // microblock maxima, running maximum, rescale factor, per-microblock constants
+            float bm[8];
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) microblock_max2(s + 32 * c4, bm[2 * c4], bm[2 * c4 + 1]);
+            const float m_new = fmaxf(fmax3(m_run, bm[0], bm[1]), fmaxf(fmax3(bm[2], bm[3], bm[4]), fmax3(bm[5], bm[6], bm[7])));
+            const bool empty = (m_new == -INFINITY);
+            const float m_cur = empty ? 0.f : m_new;
+            const float alpha = ex2_approx((m_run - m_cur) * sl2);        // m_run = -inf  ->  0
+            const float max_scaled = empty ? 0.f : fmaf(m_new, sl2, kPScaleLog2);
+            m_run = m_new;
+            float negc[8], sfv[8];
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                const bool gdead = (bm[g] == -INFINITY);
+                // sf = max(P~) / 6 = 2^(bm s - max_scaled - log2 6);  negc = -(bm s - log2 6)
+                negc[g] = gdead ? 0.f : -fmaf(bm[g], sl2, -kLog2Of6);
+                sfv[g] = gdead ? 0.f : ex2_approx(fmaf(bm[g], sl2, -max_scaled) - kLog2Of6);
+            }
+            if (dbg && j == 0) p.debug[16384 + r] = m_new;
             uint32_t codes[16];
             uint32_t sfb[2] = {0, 0};
             float rowsum = 0.f;
             // Software pipeline over the eight microblocks: the exp2 instructions of microblock g + 1 are issued
             // before the sums / conversions of microblock g, so the exp2 unit always has work queued.
-            // E = P~ / sf = 6 * 2^((S - bm) s)  with  negc = -(bm s - log2 6)
+            // E = P~ / sf = 6 * 2^((S - bm) s)
             float e[16];
             {
                 const uint64_t negc2 = pack2f(negc[0], negc[0]);
@@ -412,15 +445,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     for (int i = 0; i < 16; ++i) e[i] = en[i];
                 }
             }
-            // row sum relative to the running maximum of this block: rescale what this warpgroup has so far
-            const float a_eff = (l_run == 0.f) ? 0.f : ex2_approx(ms_prev - ms);
-            l_run = fmaf(l_run, a_eff, rowsum);
-            ms_prev = ms;
-            if (p.debug != nullptr && blockIdx.x == 0 && j == 0) p.debug[16384 + 128 + r] = rowsum;
-            PT(0)
-            // P buffer `par` was last read by the PV MMA of block j - 2
-            if (j >= 2 && !warp_wait(bar(bPV + (j - 2) % S), ((j - 2) / S) & 1, abort_flag, p.status, kWaitPEmpty)) { alive = false; break; }
+            l_run = fmaf(l_run, alpha, rowsum);
+            if (dbg && j == 0) p.debug[16384 + 128 + r] = rowsum;
+            // P buffer j & 1 was last read by the PV MMA of block j - 2
+            if (j >= 2 && !warp_wait(bar(bPV + pb), ((j >> 1) - 1) & 1, abort_flag, p.status, kWaitPEmpty)) { alive = false; break; }
             // P codes: four 16-byte chunks of the 64-byte-swizzled K-major row; scales: one word per 64-key atom
+            uint8_t* prow = sgen + C::oP + pb * C::kPBytes + r * 64;
+            uint32_t* sfp_row = reinterpret_cast<uint32_t*>(sgen + C::oSfP + pb * 1024 + (r & 31) * 16 + (r >> 5) * 4);
 #pragma unroll
             for (int c = 0; c < 4; ++c)
                 *reinterpret_cast<uint4*>(prow + ((c ^ sw) << 4)) =
@@ -428,159 +459,56 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             sfp_row[0] = sfb[0];
             sfp_row[128] = sfb[1];
             fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(bPF + par));
-            PT(3)
-        }
-        PT_DUMP(warp)
-        // hand the row sum (and the scaled maximum it refers to) to the stats warps
-        if (alive && nb > 0) {
-            s_l[par * 256 + r] = l_run;
-            s_l[par * 256 + 128 + r] = ms_prev;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(bLR));
-        }
-        __syncwarp();
-    } else {
-        reg_dealloc<96>();
-        // ------------------------------------------------------------------ stats + correction + epilogue (4 warps)
-        // Thread = row r.  For every block, ahead of the exp warps: microblock maxima of the whole row, running
-        // maximum, rescale factor and the per-microblock constants, published through shared memory.  Then O is
-        // multiplied by the rescale factor before the block's PV MMA (only when some row of the warp moved its
-        // maximum).  At the end O / l goes to global memory.
-        const int quarter = warp & 3;
-        const int r = quarter * 32 + lane;
-        const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-        const int grow = mt * kBlock + r;
-        float m_run = -INFINITY;
-        bool alive = true;
-        PT_DECL
-        // statistics of block j: constants into shared memory, rescale factor returned
-        auto do_stats = [&](int j, float& alpha_out) -> bool {
-            const int n = nb - 1 - j, bb = j & 1;
-            if (!warp_wait(bar(bQK + j % S), (j / S) & 1, abort_flag, p.status, kWaitSFull)) return false;
-            PT(0)
-            tc_fence_after();
-            const bool need_mask = ((n + 1) * kBlock > p.Nk) || (CAUSAL && (n * kBlock + kBlock - 1 > mt * kBlock + shift));
-            int lim = p.Nk - 1;
-            if (CAUSAL) lim = min(lim, grow + shift);
-            auto mask32 = [&](float* t, int c4) {
-                const int key0 = n * kBlock + c4 * 32;
+            // O row times alpha before this block's P V is added (only when a row of the warp moved its maximum);
+            // the P V MMA of block j - 1 must have landed first
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+                if (!warp_wait(bar(bPV + (pb ^ 1)), ((j - 1) >> 1) & 1, abort_flag, p.status, kWaitOReady)) { alive = false; break; }
+                tc_fence_after();
+                const uint64_t a2 = pack2f(alpha, alpha);
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (key0 + i > lim) t[i] = -INFINITY;
-            };
-            const uint32_t sa = tmem + lane_addr + (bb ? C::cS1 : C::cS0);
-            float bm[8];
-            float t0[32], t1[32];
-            // two loads in flight at a time
-            tmem_ld32(sa, t0);
-            tmem_ld32(sa + 32, t1);
-            tc_wait_ld();
-            if (need_mask) { mask32(t0, 0); mask32(t1, 1); }
-            microblock_max2(t0, bm[0], bm[1]);
-            microblock_max2(t1, bm[2], bm[3]);
-            tmem_ld32(sa + 64, t0);
-            tmem_ld32(sa + 96, t1);
-            tc_wait_ld();
-            if (need_mask) { mask32(t0, 2); mask32(t1, 3); }
-            microblock_max2(t0, bm[4], bm[5]);
-            microblock_max2(t1, bm[6], bm[7]);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(bSE + bb));
-            PT(1)
-            const float m_new = fmaxf(fmax3(m_run, bm[0], bm[1]), fmaxf(fmax3(bm[2], bm[3], bm[4]), fmax3(bm[5], bm[6], bm[7])));
-            const bool empty = (m_new == -INFINITY);
-            const float m_cur = empty ? 0.f : m_new;
-            alpha_out = ex2_approx((m_run - m_cur) * sl2);        // m_run = -inf  ->  0
-            const float max_scaled = empty ? 0.f : fmaf(m_new, sl2, kPScaleLog2);
-            float* cst = s_cst + bb * (17 * 128);
+                for (int cc = 0; cc < D / 64; ++cc) {
+                    float o0[32], o1[32];
+                    tmem_ld32(o_addr + cc * 64, o0);
+                    tmem_ld32(o_addr + cc * 64 + 32, o1);
+                    tc_wait_ld();
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                const bool gdead = (bm[g] == -INFINITY);
-                // sf = max(P~) / 6 = 2^(bm s - max_scaled - log2 6);  negc = -(bm s - log2 6)
-                cst[g * 128 + r] = gdead ? 0.f : -fmaf(bm[g], sl2, -kLog2Of6);
-                cst[(8 + g) * 128 + r] = gdead ? 0.f : ex2_approx(fmaf(bm[g], sl2, -max_scaled) - kLog2Of6);
-            }
-            cst[16 * 128 + r] = m_cur * sl2;      // scaled running maximum the exp2 values of this block refer to
-            m_run = m_new;
-            if (p.debug != nullptr && blockIdx.x == 0 && j == 0) p.debug[16384 + r] = m_new;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(bST + bb));
-            PT(2)
-            return true;
-        };
-        float alpha = 1.f;
-        if (nb > 0) alive = do_stats(0, alpha);
-        for (int j = 0; alive && j < nb; ++j) {
-            // statistics run one block ahead of the rescaling, so the exp warps never wait for a PV MMA
-            float alpha_next = 1.f;
-            if (j + 1 < nb && !do_stats(j + 1, alpha_next)) { alive = false; break; }
-            if (j > 0) {
-                if (!warp_wait(bar(bPV + (j - 1) % S), ((j - 1) / S) & 1, abort_flag, p.status, kWaitOReady)) { alive = false; break; }
-                PT(3)
-                if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-                    tc_fence_after();
-                    const uint64_t a2 = pack2f(alpha, alpha);
-#pragma unroll
-                    for (int cc = 0; cc < D / 64; ++cc) {
-                        float o0[32], o1[32];
-                        const uint32_t o_addr = tmem + lane_addr + C::cO + cc * 64;
-                        tmem_ld32(o_addr, o0);
-                        tmem_ld32(o_addr + 32, o1);
-                        tc_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            unpack2f(mul2(pack2f(o0[2 * i], o0[2 * i + 1]), a2), o0[2 * i], o0[2 * i + 1]);
-                            unpack2f(mul2(pack2f(o1[2 * i], o1[2 * i + 1]), a2), o1[2 * i], o1[2 * i + 1]);
-                        }
-                        tmem_st32(o_addr, o0);
-                        tmem_st32(o_addr + 32, o1);
+                    for (int i = 0; i < 16; ++i) {
+                        unpack2f(mul2(pack2f(o0[2 * i], o0[2 * i + 1]), a2), o0[2 * i], o0[2 * i + 1]);
+                        unpack2f(mul2(pack2f(o1[2 * i], o1[2 * i + 1]), a2), o1[2 * i], o1[2 * i + 1]);
                     }
-                    tc_wait_st();
+                    tmem_st32(o_addr + cc * 64, o0);
+                    tmem_st32(o_addr + cc * 64 + 32, o1);
                 }
+                tc_wait_st();
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(bOS));
-            alpha = alpha_next;
-            PT(4)
+            if (lane == 0) mbar_arrive(bar(bPF + pb));
+            TS(16 + 8 * t + 6, j == 20 && quarter == 0 && lane == 0)
         }
-        PT_DUMP(warp)
-        if (alive && !dead_launch) {
-            float l_tot = 0.f;
+        // ------------------------------------------------------------------ epilogue: O / l
+        if (alive && !dead_launch && t < nv) {
             if (nb > 0) {
-                alive = warp_wait(bar(bLR), 0, abort_flag, p.status, kWaitAlpha);
-                if (alive) alive = warp_wait(bar(bPV + (nb - 1) % S), ((nb - 1) / S) & 1, abort_flag, p.status, kWaitOReady);
-                if (alive) {
-                    tc_fence_after();
-                    // each exp warpgroup's sum refers to the maximum of its own last block: bring both to the final one
-                    const float ms_final = (m_run == -INFINITY ? 0.f : m_run) * sl2;
-#pragma unroll
-                    for (int w2 = 0; w2 < 2; ++w2) {
-                        const float lw = s_l[w2 * 256 + r], lm = s_l[w2 * 256 + 128 + r];
-                        if (lw != 0.f) l_tot += lw * ex2_approx(lm - ms_final);
-                    }
-                }
+                alive = warp_wait(bar(bPV + t * 2 + ((nb - 1) & 1)), ((nb - 1) >> 1) & 1, abort_flag, p.status, kWaitOReady);
+                tc_fence_after();
             }
             if (alive) {
-                const float inv_l = (l_tot == 0.f || l_tot != l_tot) ? 0.f : __frcp_rn(l_tot);
+                const float inv_l = (l_run == 0.f || l_run != l_run) ? 0.f : __frcp_rn(l_run);
                 OutT* orow = static_cast<OutT*>(p.out) + b * p.os0 + hq * p.os1 + (int64_t)grow * p.os2;
 #pragma unroll
                 for (int cc = 0; cc < D / 32; ++cc) {
                     float o[32];
                     if (nb > 0) {
-                        tmem_ld32(tmem + lane_addr + C::cO + cc * 32, o);
+                        tmem_ld32(o_addr + cc * 32, o);
                         tc_wait_ld();
                     } else {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) o[i] = 0.f;
                     }
-                    if (p.debug != nullptr && blockIdx.x == 0) {
+                    if (dbg) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) p.debug[16384 + 512 + r * D + cc * 32 + i] = o[i];
-                        if (cc == 0) p.debug[16384 + 384 + r] = l_tot;
+                        if (cc == 0) p.debug[16384 + 384 + r] = l_run;
                     }
                     if (grow < p.Nq) {
 #pragma unroll
@@ -650,7 +578,7 @@ static cudaError_t launch_t(const AttnArgs& a, const CUtensorMap& tq, const CUte
     auto kern = attn_fwd_kernel<D, CAUSAL, OutT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes);
     if (e != cudaSuccess) return e;
-    const int grid = a.B * a.Hq * (a.Nq_p / kBlock);
+    const int grid = a.B * a.Hq * ((a.Nq_p / kBlock + 1) / 2);      // one CTA per pair of query tiles
     kern<<<grid, Cfg<D>::kThreads, Cfg<D>::kSmemBytes, st>>>(tq, tk, tv, p);
     return cudaGetLastError();
 }
