@@ -2,19 +2,25 @@
 // accumulators in tensor memory, exp2 online softmax, P re-quantized to NVFP4 before the PV MMA.
 //
 // One CTA per PAIR of 128-row query tiles of one head; every K / V^T stage in shared memory serves both
-// tiles.  Three warpgroups (setmaxnreg moves registers to the softmax warpgroups):
+// tiles.  Five warpgroups (setmaxnreg moves registers to the softmax warpgroups):
 //   warp 0       TMA producer (one lane): both Q tiles once, then K (+ one delta_s row per tile) / V^T /
 //                scale atoms per KV block
 //   warp 1       Q K^T MMA issuer (one lane) and owner of the tensor-memory allocation
 //   warp 2       P V MMA issuer (one lane); warp 3 idle
-//   warps 4-7    softmax of query tile 0, warps 8-11 softmax of query tile 1: thread = row.  Per KV block the
-//                thread pulls its 128 scores out of tensor memory into registers (which frees the S buffer
-//                for the other tile at once), finds the microblock maxima and the running maximum, forms
-//                exp2 values, their row sum and the FP4 codes + E4M3 scales of P, rescales its own O row in
-//                tensor memory when the maximum moved, and finally writes O / l
-// The two softmax warpgroups own different query tiles, so neither ever waits for a value of the other: their
-// only shared resources are the single S buffer (held for one MMA + one load), the MMA issuers and the exp2
-// unit, which one warpgroup keeps busy while the other is in its load / maximum / store phases.
+//   warps 4-11   softmax of query tile 0, warps 12-19 softmax of query tile 1.  A row is shared by two threads
+//                (same lane quarter, different warpgroups): thread h owns keys [64 h, 64 h + 64) of every KV
+//                block and columns [D/2 h, D/2 (h + 1)) of the O row.
+// Per KV block a softmax thread pulls its 64 scores out of tensor memory into registers (the S buffer goes to
+// the other tile as soon as all eight warps have done so), finds its four microblock maxima and runs the exp2
+// pass at once: with E = P~ / sf = 6 * 2^((S - bm) s), the exp2 values and FP4 codes of a microblock depend
+// on the maximum bm of that microblock only.  The running row maximum enters just the E4M3 scales, the row
+// sum and the O rescale factor; the two threads of a row exchange their half maxima through shared memory
+// (published before the pass, read after it), so the exchange costs no wait.  Then the thread stores its half
+// of the P row (codes + scales), multiplies its half of the O row by the rescale factor when a row of the
+// warp moved its maximum, and at the end writes its half of O / l.
+// Tensor memory (512 columns) holds one 128-column S buffer, the two O accumulators and the scale factors; the
+// S buffer alternates between the tiles, which keeps the two tiles half a block apart: one pair of warps per
+// scheduler is in its exp2 pass while the other pair loads, reduces and stores.
 //
 // Arithmetic follows (paths inside the reference project, sageattention3_blackwell/sageattn3/blackwell/...):
 //   mainloop_tma_ws.h:509, 532-551, 865     KV blocks are walked from the last to the first
@@ -35,10 +41,15 @@
 
 namespace sage3 {
 
+// Optional per-phase cycle accounting of the first CTA (development builds only; off in the product library).
 #ifdef SAGE3_PHASE_TIMING
-#define TS(slot, cond) if (p.debug != nullptr && blockIdx.x == 0 && (cond)) p.debug[40000 + (slot)] = (float)(clock64() - *reinterpret_cast<volatile long long*>(sgen + C::oMisc + 16));
+#define PT_DECL long long pt_t = clock64(); long long pt_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define PT(i) { const long long pt_now = clock64(); pt_acc[i] += pt_now - pt_t; pt_t = pt_now; }
+#define PT_DUMP(slot) if (p.debug != nullptr && blockIdx.x == 0 && lane == 0) { for (int i_ = 0; i_ < 8; ++i_) p.debug[40000 + (slot) * 8 + i_] = (float)pt_acc[i_]; }
 #else
-#define TS(slot, cond)
+#define PT_DECL
+#define PT(i)
+#define PT_DUMP(slot)
 #endif
 
 constexpr float kLog2Of6 = 2.584962500721156f;
@@ -59,7 +70,7 @@ struct AttnParams {
 template <int D>
 struct Cfg {
     static constexpr int kStages = 6;                         // K and V^T stages, each shared by the two query tiles
-    static constexpr int kThreads = 384;                      // 3 warpgroups, see the kernel
+    static constexpr int kThreads = 640;                      // 5 warpgroups, see the kernel
     static constexpr int kQBytes = 128 * D / 2;               // per query tile
     static constexpr int kSfQkBytes = (D / 64) * 512;
     static constexpr int kKBytes = 128 * D / 2;
@@ -79,8 +90,9 @@ struct Cfg {
     static constexpr int kDeltaPitch = 512;                   // 256 B of delta_s + 256 B that stay zero
     static constexpr int oDelta = oSfP + 4 * 1024;            // [stage][tile] kDeltaPitch
     static constexpr int oOnes = oDelta + kStages * 2 * kDeltaPitch;   // 128 x 16 tile: column 0 = 1.0, rest 0
-    static constexpr int oBar = oOnes + 4096;
-    static constexpr int kNumBars = 1 + 4 * kStages + 2 + 1 + 4 + 4;
+    static constexpr int oXch = oOnes + 4096;                 // float [2 parities][tile][half][128]: microblock-half maxima; [tile][half][128] row sums
+    static constexpr int oBar = oXch + (8 + 4) * 128 * 4;
+    static constexpr int kNumBars = 1 + 4 * kStages + 2 + 1 + 4 + 4 + 8;
     static constexpr int oMisc = oBar + kNumBars * 8;
     static constexpr int kSmemBytes = oMisc + 64 + 1024;      // + slack for the manual 1024-byte alignment
     // tensor-memory columns: one S buffer, one O accumulator per tile, scale factors
@@ -135,7 +147,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // barriers
     auto bar = [&](int i) { return sbase + C::oBar + 8u * i; };
     const int bQ = 0, bKF = 1, bKE = bKF + S, bVF = bKE + S, bVE = bVF + S, bSF = bVE + S, bSE = bSF + 2,
-              bPF = bSE + 1, bPV = bPF + 4;
+              bPF = bSE + 1, bPV = bPF + 4, bXC = bPV + 4;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + C::oMisc);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + C::oMisc + 8);
 
@@ -164,9 +176,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int nbmax = max(nbt[0], nbt[1]);
     const int skip[2] = {nbmax - nbt[0], nbmax - nbt[1]};
 
-#ifdef SAGE3_PHASE_TIMING
-    if (threadIdx.x == 0) *reinterpret_cast<volatile long long*>(sgen + C::oMisc + 16) = clock64();
-#endif
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         mbar_init(bar(bQ), 1);
@@ -178,11 +187,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         mbar_init(bar(bSF), 1);            // S holds the scores of tile 0's next block
         mbar_init(bar(bSF + 1), 1);        // ... of tile 1's next block
-        mbar_init(bar(bSE), 4);            // the four warps of the tile that owns S have it in registers
+        mbar_init(bar(bSE), 8);            // the eight warps of the tile that owns S have it in registers
         for (int i = 0; i < 4; ++i) {
-            mbar_init(bar(bPF + i), 4);    // [tile][buffer]: P (+ scales) written and O rescaled
+            mbar_init(bar(bPF + i), 8);    // [tile][buffer]: P (+ scales) written and O rescaled
             mbar_init(bar(bPV + i), 1);    // [tile][buffer]: the P V MMA that read it is complete
         }
+        for (int i = 0; i < 8; ++i) mbar_init(bar(bXC + i), 2);   // [tile][lane quarter]: both half-row warps have published a value
         mbar_fence_init();
     }
     {
@@ -213,10 +223,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
     const float sl2 = p.sm_scale_per_head ? p.sm_scale_per_head[hq] * 1.4426950408889634f : p.sm_scale_log2;
 
-    // Register budget: 384 threads start with 168 registers each; the softmax warpgroups (a whole S row per
-    // thread) take what warpgroup 0 (three single-lane roles) does not need.
+    // Register budget: 640 threads start with 96 registers each, and that allocation (61 440) is all the CTA can
+    // ever hold: 128 x 32 for warpgroup 0 (three single-lane roles) + 512 x 112 for the softmax warpgroups.
+    // (An increase beyond the launch allocation would wait forever.)
     if (warp < 4) {
-      reg_dealloc<48>();
+      reg_dealloc<32>();
       if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0 && nbmax > 0) {
@@ -265,9 +276,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             int uses = 0;
             for (int jj = 0; ok && jj < nbmax; ++jj) {
                 const int st = jj % S;
-                TS(0, jj == 20)
                 if (!mbar_wait(bar(bKF + st), (jj / S) & 1, abort_flag, p.status, kWaitKFull)) { ok = false; break; }
-                TS(1, jj == 20)
                 tc_fence_after();
                 const uint64_t k_desc = make_sdesc(sbase + C::oK + st * 8192, 16, C::kSboQK, C::kSwzQK);
 #pragma unroll
@@ -275,9 +284,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     tc_cp_sf(tmem + C::cSfK + 4 * ks, make_sdesc(sbase + C::oSfK + st * 1024 + ks * 512, 0, 128, kSwzNone));
                 for (int t = 0; t < 2; ++t) {
                     if (jj < skip[t]) continue;
-                    TS(2 + 4 * t, jj == 20)
                     if (uses > 0 && !mbar_wait(bar(bSE), (uses - 1) & 1, abort_flag, p.status, kWaitSEmpty)) { ok = false; break; }
-                    TS(3 + 4 * t, jj == 20)
                     tc_fence_after();
                     const uint64_t q_desc = make_sdesc(sbase + C::oQ + t * 8192, 16, C::kSboQK, C::kSwzQK);
                     // S <- 1 (x) delta_s: A = [128 x 16] with ones in column 0 (K-major), B = the delta_s row read as an
@@ -288,9 +295,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     for (int ks = 0; ks < D / 64; ++ks)
                         tc_mma_nvfp4(tmem + C::cS, q_desc + 2 * ks, k_desc + 2 * ks, idesc_qk,
                                      tmem + C::cSfQ + 8 * t + 4 * ks, tmem + C::cSfK + 4 * ks, true);
-                    TS(4 + 4 * t, jj == 20)
                     tc_commit(bar(bSF + t));
-                    TS(5 + 4 * t, jj == 20)
                     ++uses;
                 }
                 if (ok) tc_commit(bar(bKE + st));
@@ -334,98 +339,82 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         __syncwarp();
       }   // warp 3: no role (it completes warpgroup 0 so that it can give its registers away)
     } else {
-        reg_alloc<224>();
-        // ------------------------------------------------------------------ softmax warpgroups (2 x 4 warps)
-        // Warpgroup t owns query tile t: thread = row r, with the row's running maximum, row sum and O row.
-        const int t = (warp >> 2) - 1;
+        reg_alloc<112>();
+        // ------------------------------------------------------------------ softmax warpgroups (4 x 4 warps)
+        // Warpgroups 2 t and 2 t + 1 own query tile t; a row is shared by two threads (same lane quarter, one in
+        // each warpgroup): thread `h` handles keys [64 h, 64 h + 64) of every block and columns [D/2 h, D/2 (h+1))
+        // of the O row.  The two exchange the maximum of their halves once per block; everything else (exp2
+        // pass, codes and scales of P, partial row sum, O rescale) is private.  Four such warps share a
+        // scheduler, so the exp2 unit finds work while others load, reduce or store.
+        const int wg = (warp >> 2) - 1;
+        const int t = wg >> 1, h = wg & 1;
         const int quarter = warp & 3;            // tensor-memory lane quarter this warp may touch
         const int r = quarter * 32 + lane;       // row inside the tile
         const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
         const int mt = mt0 + t;
         const int nb = nbt[t];
         const int grow = mt * kBlock + r;        // query index
-        const uint32_t s_addr = tmem + lane_addr + C::cS;
-        const uint32_t o_addr = tmem + lane_addr + C::cO + t * 128;
+        const uint32_t s_addr = tmem + lane_addr + C::cS + 64 * h;
+        const uint32_t o_addr = tmem + lane_addr + C::cO + t * 128 + (D / 2) * h;
         const int sw = (r >> 1) & 3;
         const uint64_t sl2x2 = pack2f(sl2, sl2);
         const bool dbg = (p.debug != nullptr && blockIdx.x == 0 && t == 0);
+        float* xch_mine = reinterpret_cast<float*>(sgen + C::oXch) + (t * 2 + h) * 128 + r;
+        const float* xch_other = reinterpret_cast<float*>(sgen + C::oXch) + (t * 2 + (h ^ 1)) * 128 + r;
+        const uint32_t bar_x = bar(bXC + t * 4 + quarter);
+        int xphase = 0;
         float m_run = -INFINITY, l_run = 0.f;
         bool alive = true;
+        PT_DECL
         for (int j = 0; j < nb; ++j) {
             const int n = nb - 1 - j, pb = t * 2 + (j & 1);
-            TS(16 + 8 * t + 0, j == 20 && quarter == 0 && lane == 0)
             if (!warp_wait(bar(bSF + t), j & 1, abort_flag, p.status, kWaitSFull)) { alive = false; break; }
-            TS(16 + 8 * t + 1, j == 20 && quarter == 0 && lane == 0)
+            PT(0)
             tc_fence_after();
-            float s[128];
-#pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) tmem_ld32(s_addr + c4 * 32, s + c4 * 32);
+            float s[64];
+            tmem_ld32(s_addr, s);
+            tmem_ld32(s_addr + 32, s + 32);
             tc_wait_ld();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(bSE));     // S is in registers: the other tile's Q K^T may overwrite it
-            TS(16 + 8 * t + 2 + quarter, j == 20 && lane == 0)
+            PT(1)
             const bool need_mask = ((n + 1) * kBlock > p.Nk) || (CAUSAL && (n * kBlock + kBlock - 1 > mt * kBlock + shift));
             if (need_mask) {
                 int lim = p.Nk - 1;
                 if (CAUSAL) lim = min(lim, grow + shift);
-                const int key0 = n * kBlock;
+                const int key0 = n * kBlock + 64 * h;
 #pragma unroll
-                for (int i = 0; i < 128; ++i)
+                for (int i = 0; i < 64; ++i)
                     if (key0 + i > lim) s[i] = -INFINITY;
             }
             if (dbg && j == 0) {
 #pragma unroll
-                for (int i = 0; i < 128; ++i) p.debug[r * 128 + i] = s[i];
+                for (int i = 0; i < 64; ++i) p.debug[r * 128 + 64 * h + i] = s[i];
             }
-            // microblock maxima, running maximum, rescale factor, per-microblock constants
-            float bm[8];
+            // microblock maxima of this half; the half maximum goes to the partner thread
+            float bm[4];
+            microblock_max2(s, bm[0], bm[1]);
+            microblock_max2(s + 32, bm[2], bm[3]);
+            const float m_half = fmaxf(fmaxf(bm[0], bm[1]), fmaxf(bm[2], bm[3]));
+            xch_mine[(j & 1) * 512] = m_half;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_x);
+            PT(2)
+            // exp2 pass: E = P~ / sf = 6 * 2^((S - bm) s) needs the microblock maximum only, not the row maximum
+            uint32_t codes[8];
+            float se[4];
 #pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) microblock_max2(s + 32 * c4, bm[2 * c4], bm[2 * c4 + 1]);
-            const float m_new = fmaxf(fmax3(m_run, bm[0], bm[1]), fmaxf(fmax3(bm[2], bm[3], bm[4]), fmax3(bm[5], bm[6], bm[7])));
-            const bool empty = (m_new == -INFINITY);
-            const float m_cur = empty ? 0.f : m_new;
-            const float alpha = ex2_approx((m_run - m_cur) * sl2);        // m_run = -inf  ->  0
-            const float max_scaled = empty ? 0.f : fmaf(m_new, sl2, kPScaleLog2);
-            m_run = m_new;
-            float negc[8], sfv[8];
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                const bool gdead = (bm[g] == -INFINITY);
-                // sf = max(P~) / 6 = 2^(bm s - max_scaled - log2 6);  negc = -(bm s - log2 6)
-                negc[g] = gdead ? 0.f : -fmaf(bm[g], sl2, -kLog2Of6);
-                sfv[g] = gdead ? 0.f : ex2_approx(fmaf(bm[g], sl2, -max_scaled) - kLog2Of6);
-            }
-            if (dbg && j == 0) p.debug[16384 + r] = m_new;
-            uint32_t codes[16];
-            uint32_t sfb[2] = {0, 0};
-            float rowsum = 0.f;
-            // Software pipeline over the eight microblocks: the exp2 instructions of microblock g + 1 are issued
-            // before the sums / conversions of microblock g, so the exp2 unit always has work queued.
-            // E = P~ / sf = 6 * 2^((S - bm) s)
-            float e[16];
-            {
-                const uint64_t negc2 = pack2f(negc[0], negc[0]);
+            for (int g = 0; g < 4; ++g) {
+                const float negc = (bm[g] == -INFINITY) ? 0.f : -fmaf(bm[g], sl2, -kLog2Of6);
+                const uint64_t negc2 = pack2f(negc, negc);
+                float e[16];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     float a, b2;
-                    unpack2f(fma2(pack2f(s[2 * i], s[2 * i + 1]), sl2x2, negc2), a, b2);
+                    unpack2f(fma2(pack2f(s[16 * g + 2 * i], s[16 * g + 2 * i + 1]), sl2x2, negc2), a, b2);
                     e[2 * i] = ex2_approx(a);
                     e[2 * i + 1] = ex2_approx(b2);
-                }
-            }
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                float en[16];
-                if (g < 7) {
-                    const uint64_t negc2 = pack2f(negc[g + 1], negc[g + 1]);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        float a, b2;
-                        unpack2f(fma2(pack2f(s[16 * (g + 1) + 2 * i], s[16 * (g + 1) + 2 * i + 1]), sl2x2, negc2), a, b2);
-                        en[2 * i] = ex2_approx(a);
-                        en[2 * i + 1] = ex2_approx(b2);
-                    }
                 }
                 uint64_t acc0 = pack2f(e[0], e[1]), acc1 = pack2f(e[2], e[3]);
                 acc0 = add2(acc0, pack2f(e[4], e[5]));
@@ -436,67 +425,87 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 acc1 = add2(acc1, pack2f(e[14], e[15]));
                 float se0, se1;
                 unpack2f(add2(acc0, acc1), se0, se1);
-                rowsum = fmaf(sfv[g], se0 + se1, rowsum);
+                se[g] = se0 + se1;
                 codes[2 * g] = cvt_e2m1x8(e[0], e[1], e[2], e[3], e[4], e[5], e[6], e[7]);
                 codes[2 * g + 1] = cvt_e2m1x8(e[8], e[9], e[10], e[11], e[12], e[13], e[14], e[15]);
-                sfb[g >> 2] |= (cvt_e4m3x2(sfv[g], 0.f) & 0xffu) << (8 * (g & 3));
-                if (g < 7) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) e[i] = en[i];
-                }
             }
-            l_run = fmaf(l_run, alpha, rowsum);
-            if (dbg && j == 0) p.debug[16384 + 128 + r] = rowsum;
+            PT(3)
+            // running maximum (with the partner's half, published before its own exp2 pass), rescale factor,
+            // E4M3 scale sf = max(P~) / 6 = 2^(bm s - max_scaled - log2 6) of every microblock, weighted sum
+            if (!warp_wait(bar_x, xphase, abort_flag, p.status, kWaitPair)) { alive = false; break; }
+            xphase ^= 1;
+            const float m_new = fmax3(m_run, m_half, xch_other[(j & 1) * 512]);
+            const bool empty = (m_new == -INFINITY);
+            const float m_cur = empty ? 0.f : m_new;
+            const float alpha = ex2_approx((m_run - m_cur) * sl2);        // m_run = -inf  ->  0
+            const float max_scaled = empty ? 0.f : fmaf(m_new, sl2, kPScaleLog2);
+            m_run = m_new;
+            if (dbg && j == 0 && h == 0) p.debug[16384 + r] = m_new;
+            uint32_t sfb = 0;
+            float rowsum = 0.f;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const float sfv = (bm[g] == -INFINITY) ? 0.f : ex2_approx(fmaf(bm[g], sl2, -max_scaled) - kLog2Of6);
+                rowsum = fmaf(sfv, se[g], rowsum);
+                sfb |= (cvt_e4m3x2(sfv, 0.f) & 0xffu) << (8 * g);
+            }
+            l_run = fmaf(l_run, alpha, rowsum);      // partial row sum of this thread's keys
+            if (dbg && j == 0) p.debug[16384 + 128 + 128 * h + r] = rowsum;
             // P buffer j & 1 was last read by the PV MMA of block j - 2
             if (j >= 2 && !warp_wait(bar(bPV + pb), ((j >> 1) - 1) & 1, abort_flag, p.status, kWaitPEmpty)) { alive = false; break; }
-            // P codes: four 16-byte chunks of the 64-byte-swizzled K-major row; scales: one word per 64-key atom
+            PT(4)
+            // P codes: this half's two 16-byte chunks of the 64-byte-swizzled K-major row; scales: its 64-key atom
             uint8_t* prow = sgen + C::oP + pb * C::kPBytes + r * 64;
             uint32_t* sfp_row = reinterpret_cast<uint32_t*>(sgen + C::oSfP + pb * 1024 + (r & 31) * 16 + (r >> 5) * 4);
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-                *reinterpret_cast<uint4*>(prow + ((c ^ sw) << 4)) =
+            for (int c = 0; c < 2; ++c)
+                *reinterpret_cast<uint4*>(prow + (((2 * h + c) ^ sw) << 4)) =
                     make_uint4(codes[4 * c], codes[4 * c + 1], codes[4 * c + 2], codes[4 * c + 3]);
-            sfp_row[0] = sfb[0];
-            sfp_row[128] = sfb[1];
+            sfp_row[128 * h] = sfb;
             fence_proxy_async_smem();
-            // O row times alpha before this block's P V is added (only when a row of the warp moved its maximum);
-            // the P V MMA of block j - 1 must have landed first
+            PT(5)
+            // This thread's half of the O row times alpha before the block's P V is added (only when a row of the
+            // warp moved its maximum); the P V MMA of block j - 1 must have landed first
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
                 if (!warp_wait(bar(bPV + (pb ^ 1)), ((j - 1) >> 1) & 1, abort_flag, p.status, kWaitOReady)) { alive = false; break; }
                 tc_fence_after();
                 const uint64_t a2 = pack2f(alpha, alpha);
 #pragma unroll
                 for (int cc = 0; cc < D / 64; ++cc) {
-                    float o0[32], o1[32];
-                    tmem_ld32(o_addr + cc * 64, o0);
-                    tmem_ld32(o_addr + cc * 64 + 32, o1);
+                    float o0[32];
+                    tmem_ld32(o_addr + cc * 32, o0);
                     tc_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
+                    for (int i = 0; i < 16; ++i)
                         unpack2f(mul2(pack2f(o0[2 * i], o0[2 * i + 1]), a2), o0[2 * i], o0[2 * i + 1]);
-                        unpack2f(mul2(pack2f(o1[2 * i], o1[2 * i + 1]), a2), o1[2 * i], o1[2 * i + 1]);
-                    }
-                    tmem_st32(o_addr + cc * 64, o0);
-                    tmem_st32(o_addr + cc * 64 + 32, o1);
+                    tmem_st32(o_addr + cc * 32, o0);
                 }
                 tc_wait_st();
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(bPF + pb));
-            TS(16 + 8 * t + 6, j == 20 && quarter == 0 && lane == 0)
+            PT(6)
         }
+        PT_DUMP(warp)
         // ------------------------------------------------------------------ epilogue: O / l
         if (alive && !dead_launch && t < nv) {
-            if (nb > 0) {
+            // the row sum is the sum of the two threads' partial sums (both refer to the same running maximum)
+            float* lx = reinterpret_cast<float*>(sgen + C::oXch) + 8 * 128;
+            lx[(t * 2 + h) * 128 + r] = l_run;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_x);
+            alive = warp_wait(bar_x, xphase, abort_flag, p.status, kWaitPair);
+            const float l_tot = l_run + lx[(t * 2 + (h ^ 1)) * 128 + r];
+            if (alive && nb > 0) {
                 alive = warp_wait(bar(bPV + t * 2 + ((nb - 1) & 1)), ((nb - 1) >> 1) & 1, abort_flag, p.status, kWaitOReady);
                 tc_fence_after();
             }
             if (alive) {
-                const float inv_l = (l_run == 0.f || l_run != l_run) ? 0.f : __frcp_rn(l_run);
-                OutT* orow = static_cast<OutT*>(p.out) + b * p.os0 + hq * p.os1 + (int64_t)grow * p.os2;
+                const float inv_l = (l_tot == 0.f || l_tot != l_tot) ? 0.f : __frcp_rn(l_tot);
+                OutT* orow = static_cast<OutT*>(p.out) + b * p.os0 + hq * p.os1 + (int64_t)grow * p.os2 + (D / 2) * h;
 #pragma unroll
-                for (int cc = 0; cc < D / 32; ++cc) {
+                for (int cc = 0; cc < D / 64; ++cc) {
                     float o[32];
                     if (nb > 0) {
                         tmem_ld32(o_addr + cc * 32, o);
@@ -507,8 +516,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     }
                     if (dbg) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) p.debug[16384 + 512 + r * D + cc * 32 + i] = o[i];
-                        if (cc == 0) p.debug[16384 + 384 + r] = l_run;
+                        for (int i = 0; i < 32; ++i) p.debug[16384 + 512 + r * D + (D / 2) * h + cc * 32 + i] = o[i];
+                        if (cc == 0 && h == 0) p.debug[16384 + 384 + r] = l_tot;
                     }
                     if (grow < p.Nq) {
 #pragma unroll
