@@ -354,12 +354,12 @@ def main():
     ms_per_step = total_ms / args.steps
     att_tops = flops / (att_ms * 1e-3) / 1e12
     fp4_peak = 4.0 * peaks["bf16_sustained"]          # dense FP4 is 4x dense bf16 on this part
-    # DRAM traffic of one attention launch: ncu measured 163.1 MB (dram__bytes_read.sum + dram__bytes_write.sum) on
+    # DRAM traffic of one attention launch: ncu measured 159.6 MB (dram__bytes_read.sum + dram__bytes_write.sum) on
     # the ncu_small case (16 heads x 16384 tokens, D=128; profiles/attn_fwd_kernel__ncu_small.md); the kernel reads
     # each head's operands once from DRAM and writes its output once, so traffic scales with B*H*N*D.
     traffic, traffic_src = None, None
     if D == 128 and not w["causal"]:
-        traffic = 163.1e6 * (B * Hq * Nq) / (16 * 16384.0)
+        traffic = 159.6e6 * (B * Hq * Nq) / (16 * 16384.0)
         traffic_src = "scaled from one ncu capture of the ncu_small case in proportion to B*H*N"
     line = dict(
         metric="attention TOPS (4*B*H*Nq*Nk*D/t) of the smooth+NVFP4-quantize+attend path", value=world * flops / (ms_per_step * 1e-3) / 1e12,

@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define SAGE3_ABI_VERSION 1
+#define SAGE3_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define SAGE3_API __attribute__((visibility("default")))
@@ -81,9 +81,11 @@ typedef struct Sage3Desc {
  *   k_codes, k_sf                             same for K (kv heads), natural token order
  *   v_codes  u8   [B][Hkv][D][Nk_p/2]         V transposed, microblocks of 16 consecutive tokens
  *   v_sf     u8   [B][Hkv][Nk_p/128][2][512]  atoms with r = channel, c = (token % 128) / 16
+ *   qkm      fp32 [B][Hq][Nq_p]               q . km per query row (the part of q k^T that K smoothing removes;
+ *                                             core.py:289-293 `lse_correction`), used by the LSE output
  */
 typedef struct Sage3Workspace {
-    size_t status, kpart, km, qm, delta, q_codes, q_sf, k_codes, k_sf, v_codes, v_sf;
+    size_t status, kpart, km, qm, delta, q_codes, q_sf, k_codes, k_sf, v_codes, v_sf, qkm;
     size_t total_bytes;
     int32_t nq_pad, nk_pad, nqm, kchunks;
 } Sage3Workspace;
@@ -114,7 +116,9 @@ SAGE3_API int sage3_prepass(const Sage3Desc* desc, const void* q, const void* k,
  * Attention over a workspace filled by sage3_prepass with the same `desc`: out[b][h][n][d] in `dtype`
  * with the strides of desc->o_stride.  Replaces fp4attn_cuda.fwd (blackwell/api.cu:203-341) and the
  * final slice of api.py:151 (rows beyond Nq are never written).
- * `lse` is reserved for a natural-log log-sum-exp output [B][Hq][Nq] and must be NULL for now.
+ * `lse`: NULL, or a device array fp32 [B][Hq][Nq] that receives the natural-log log-sum-exp of the scaled scores
+ * of every query row, ln sum_k exp(sm_scale * q.k), computed from the quantized scores plus sm_scale * q.km as
+ * sageattention/core.py:327 does for its kernels (-inf for a row without visible keys).
  */
 SAGE3_API int sage3_attn_fwd(const Sage3Desc* desc, void* ws, void* out, float* lse, void* stream);
 

@@ -284,13 +284,50 @@ def _to_hnd(x: torch.Tensor, tensor_layout: str) -> torch.Tensor:
     raise ValueError(f"unknown tensor_layout {tensor_layout!r}")
 
 
+def lse_from_parts(pp: Prepass, q: torch.Tensor, m: torch.Tensor, l: torch.Tensor, sm_scale=None) -> torch.Tensor:
+    """ln sum_k exp(sm_scale * q.k) per query row, [B,Hq,Nq] fp32, from the running maximum m and row sum l of the
+    quantized, smoothed scores plus sm_scale * q.km, the part K smoothing took out of every score of the row
+    (sageattention/core.py:289-293, 327: `lse / 1.44269504 + lse_correction * sm_scale`).  q: [B,Hq,Nq,D]."""
+    B, Hq, Nq, D = q.shape
+    s2 = _scale_log2(sm_scale, Hq, D).view(1, Hq, 1)
+    group = Hq // pp.km.shape[1]
+    km = pp.km.to(torch.float32).repeat_interleave(group, dim=1) if group > 1 else pp.km.to(torch.float32)
+    qkm = torch.einsum("bhnd,bhd->bhn", q.to(torch.float32), km)
+    m, l = m.squeeze(-1), l.squeeze(-1)
+    m_cur = torch.where(torch.isfinite(m), m, torch.zeros_like(m))
+    lse2 = m_cur * s2 + torch.log2(l) + P_SCALE_LOG2            # l = 2688 * sum_k 2^((S_k - m) s)
+    lse = lse2 / LOG2E + (s2 / LOG2E) * qkm
+    return torch.where(l == 0, torch.full_like(lse, -math.inf), lse)
+
+
 def sageattn3_oracle(q, k, v, tensor_layout: str = "HND", is_causal: bool = False, sm_scale=None,
-                     per_block_mean: bool = True) -> torch.Tensor:
-    """Whole pipeline (api.py:131-152) on CPU tensors; returns the output in the caller's layout."""
+                     per_block_mean: bool = True, return_lse: bool = False):
+    """Whole pipeline (api.py:131-152) on CPU tensors; returns the output in the caller's layout
+    (and the [B,Hq,Nq] log-sum-exp when `return_lse`)."""
     qh, kh, vh = (_to_hnd(t, tensor_layout) for t in (q, k, v))
     pp = prepass(qh, kh, vh, per_block_mean)
+    if return_lse:
+        o, m, l = attention_from_prepass(pp, is_causal, sm_scale, return_lse_parts=True)
+        lse = lse_from_parts(pp, qh, m, l, sm_scale)
+        return (o if tensor_layout == "HND" else o.transpose(1, 2)), lse
     o = attention_from_prepass(pp, is_causal, sm_scale)
     return o if tensor_layout == "HND" else o.transpose(1, 2)
+
+
+def fp32_lse(q, k, tensor_layout: str = "HND", is_causal: bool = False, sm_scale=None) -> torch.Tensor:
+    """ln sum_k exp(sm_scale * q.k) in fp32 from the unquantized inputs, [B,Hq,Nq]."""
+    qh, kh = (_to_hnd(t, tensor_layout).to(torch.float32) for t in (q, k))
+    B, Hq, Nq, D = qh.shape
+    Hkv, Nk = kh.shape[1], kh.shape[2]
+    if Hq != Hkv:
+        kh = kh.repeat_interleave(Hq // Hkv, dim=1)
+    s = _scale_log2(sm_scale, Hq, D).view(1, Hq, 1, 1) / LOG2E
+    S = torch.matmul(qh, kh.transpose(-1, -2)) * s
+    if is_causal:
+        i = torch.arange(Nq).view(-1, 1)
+        j = torch.arange(Nk).view(1, -1)
+        S = S.masked_fill(j > i + (Nk - Nq), -math.inf)
+    return torch.logsumexp(S, dim=-1)
 
 
 def fp32_attention(q, k, v, tensor_layout: str = "HND", is_causal: bool = False, sm_scale=None) -> torch.Tensor:

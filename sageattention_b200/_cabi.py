@@ -29,7 +29,7 @@ class Sage3Desc(C.Structure):
 class Sage3Workspace(C.Structure):
     _fields_ = [(n, C.c_size_t) for n in
                 ("status", "kpart", "km", "qm", "delta", "q_codes", "q_sf", "k_codes", "k_sf", "v_codes", "v_sf",
-                 "total_bytes")] + [(n, C.c_int32) for n in ("nq_pad", "nk_pad", "nqm", "kchunks")]
+                 "qkm", "total_bytes")] + [(n, C.c_int32) for n in ("nq_pad", "nk_pad", "nqm", "kchunks")]
 
 
 class Sage3Error(RuntimeError):

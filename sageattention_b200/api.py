@@ -50,7 +50,7 @@ class Sage3Problem:
     """Shapes, strides and workspace of one call; reusable while shapes, strides and dtype stay the same."""
 
     def __init__(self, q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, per_block_mean=True,
-                 out: torch.Tensor | None = None, workspace: torch.Tensor | None = None):
+                 out: torch.Tensor | None = None, workspace: torch.Tensor | None = None, return_lse: bool = False):
         if tensor_layout not in ("HND", "NHD"):
             raise ValueError(f"tensor_layout must be 'HND' or 'NHD', got {tensor_layout!r}")
         for name, t in (("q", q), ("k", k), ("v", v)):
@@ -81,6 +81,8 @@ class Sage3Problem:
         elif out.shape != q.shape or out.dtype != q.dtype or not _usable(out):
             raise ValueError("out must match q in shape and dtype, with 16-byte aligned rows")
         self.out = out
+        # natural-log log-sum-exp of the scaled scores per query row, [B, Hq, Nq] fp32 (sageattention/core.py:327)
+        self.lse = torch.empty(B, Hq, Nq, dtype=torch.float32, device=q.device) if return_lse else None
         self.tensor_layout = tensor_layout
         self.device = q.device
 
@@ -126,11 +128,14 @@ class Sage3Problem:
                                                   self.v.data_ptr(), self.ws.buf.data_ptr(), self._stream()),
                         "sage3_prepass")
 
+    def _lse_ptr(self):
+        return None if self.lse is None else self.lse.data_ptr()
+
     def attention(self, debug: torch.Tensor | None = None) -> torch.Tensor:
         with torch.cuda.device(self.device):
             if debug is None:
-                rc = _cabi.lib().sage3_attn_fwd(C.byref(self.desc), self.ws.buf.data_ptr(), self.out.data_ptr(), None,
-                                                self._stream())
+                rc = _cabi.lib().sage3_attn_fwd(C.byref(self.desc), self.ws.buf.data_ptr(), self.out.data_ptr(),
+                                                self._lse_ptr(), self._stream())
             else:
                 rc = _cabi.lib().sage3_attn_fwd_debug(C.byref(self.desc), self.ws.buf.data_ptr(), self.out.data_ptr(),
                                                       debug.data_ptr(), self._stream())
@@ -140,8 +145,8 @@ class Sage3Problem:
     def run(self) -> torch.Tensor:
         with torch.cuda.device(self.device):
             _cabi.check(_cabi.lib().sage3_fwd(C.byref(self.desc), self.q.data_ptr(), self.k.data_ptr(),
-                                              self.v.data_ptr(), self.ws.buf.data_ptr(), self.out.data_ptr(), None,
-                                              self._stream()), "sage3_fwd")
+                                              self.v.data_ptr(), self.ws.buf.data_ptr(), self.out.data_ptr(),
+                                              self._lse_ptr(), self._stream()), "sage3_fwd")
         return self.out
 
     def check_status(self) -> int:
@@ -165,15 +170,19 @@ def sageattn3(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: 
     may be a float or a tensor with one scale per query head.  Extra keyword arguments (dropout_p, scale, ...)
     are accepted and ignored, as the reference does, so the function can replace
     F.scaled_dot_product_attention in place.
+
+    With `return_lse=True` the result is `(out, lse)`, lse = ln sum_k exp(sm_scale * q.k) per query row as fp32
+    [B, Hq, Nq] (the keyword and meaning of sageattention/core.py:86, 327): taken from the quantized scores plus
+    sm_scale * q.mean(k), the part of the scores that K smoothing removes.
     """
     if attn_mask is not None:
         raise NotImplementedError("attn_mask is not supported by the FP4 attention path")
-    if return_lse:
-        raise NotImplementedError("return_lse is not available yet (the reference's FP4 kernel never writes its LSE either)")
     if sm_scale is None and kwargs.get("scale") is not None:
         sm_scale = kwargs["scale"]          # F.scaled_dot_product_attention's name for the same thing
-    prob = Sage3Problem(q, k, v, tensor_layout, is_causal, sm_scale, per_block_mean, workspace=workspace)
-    return prob.run()
+    prob = Sage3Problem(q, k, v, tensor_layout, is_causal, sm_scale, per_block_mean, workspace=workspace,
+                        return_lse=return_lse)
+    out = prob.run()
+    return (out, prob.lse) if return_lse else out
 
 
 def sageattn3_blackwell(q, k, v, attn_mask=None, is_causal=False, per_block_mean=True, **kwargs):

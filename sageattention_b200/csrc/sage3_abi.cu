@@ -53,6 +53,7 @@ int layout(const Sage3Desc* d, Sage3Workspace* w) {
     w->k_sf = off;    off += align_up(B * Hkv * (nkp / 128) * (D / 64) * 512);
     w->v_codes = off; off += align_up(B * Hkv * D * (nkp / 2));
     w->v_sf = off;    off += align_up(B * Hkv * (nkp / 128) * 1024);
+    w->qkm = off;     off += align_up(B * Hq * nqp * sizeof(float));
     w->total_bytes = off;
     w->nq_pad = (int32_t)nqp;
     w->nk_pad = (int32_t)nkp;
@@ -76,7 +77,7 @@ int attn_impl(const Sage3Desc* desc, void* ws, void* out, float* lse, float* deb
     int rc = layout(desc, &w);
     if (rc != SAGE3_OK) return rc;
     if (!ws || !out) return SAGE3_E_NULL;
-    if (lse != nullptr) return SAGE3_E_SHAPE;   // reserved
+    if (lse != nullptr && !aligned(lse, 4)) return SAGE3_E_ALIGN;
     if (!aligned(ws, kWsAlign) || !aligned(out, 16)) return SAGE3_E_ALIGN;
     rc = check_arch();
     if (rc != SAGE3_OK) return rc;
@@ -95,6 +96,8 @@ int attn_impl(const Sage3Desc* desc, void* ws, void* out, float* lse, float* deb
     a.k_codes = base + w.k_codes; a.k_sf = base + w.k_sf;
     a.v_codes = base + w.v_codes; a.v_sf = base + w.v_sf;
     a.out = out;
+    a.lse = lse;
+    a.qkm = reinterpret_cast<const float*>(base + w.qkm);
     for (int i = 0; i < 3; ++i) a.os[i] = desc->o_stride[i];
     a.status = reinterpret_cast<int*>(base + w.status);
     a.debug = debug;
@@ -126,7 +129,7 @@ SAGE3_API const char* sage3_strerror(int code) {
     switch (code) {
         case SAGE3_OK: return "ok";
         case SAGE3_E_NULL: return "a required pointer is NULL";
-        case SAGE3_E_SHAPE: return "unsupported shape (D must be 64 or 128, Hq a multiple of Hkv, sizes positive, lse NULL)";
+        case SAGE3_E_SHAPE: return "unsupported shape (D must be 64 or 128, Hq a multiple of Hkv, sizes positive)";
         case SAGE3_E_DTYPE: return "dtype must be SAGE3_FP16 or SAGE3_BF16";
         case SAGE3_E_STRIDE: return "strides must be non-negative multiples of 8 elements with the last dimension contiguous";
         case SAGE3_E_ALIGN: return "pointer alignment: tensors 16 bytes, workspace 256 bytes";
@@ -172,6 +175,7 @@ SAGE3_API int sage3_prepass(const Sage3Desc* desc, const void* q, const void* k,
     a.q_codes = base + w.q_codes; a.q_sf = base + w.q_sf;
     a.k_codes = base + w.k_codes; a.k_sf = base + w.k_sf;
     a.v_codes = base + w.v_codes; a.v_sf = base + w.v_sf;
+    a.qkm = reinterpret_cast<float*>(base + w.qkm);
     a.status = reinterpret_cast<int*>(base + w.status);
     if (cudaMemsetAsync(base + w.status, 0, 64 * sizeof(int32_t), static_cast<cudaStream_t>(stream)) != cudaSuccess) return SAGE3_E_CUDA;
     return sage3::launch_prepass(a, static_cast<cudaStream_t>(stream)) == cudaSuccess ? SAGE3_OK : SAGE3_E_CUDA;

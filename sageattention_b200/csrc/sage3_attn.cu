@@ -63,6 +63,9 @@ struct AttnParams {
     const uint16_t* delta;              // 16-bit elements [B*Hq][nqm][nkb*128]
     void* out;
     int64_t os0, os1, os2;
+    float* lse;                         // optional fp32 [B*Hq][Nq]
+    const float* qkm;                   // fp32 [B*Hq][nqt*128]: q . km per query row
+    float sm_scale;
     int* status;
     float* debug;                       // optional dump of CTA 0, tile 0 (nullptr in normal use)
 };
@@ -501,6 +504,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 alive = warp_wait(bar(bPV + t * 2 + ((nb - 1) & 1)), ((nb - 1) >> 1) & 1, abort_flag, p.status, kWaitOReady);
                 tc_fence_after();
             }
+            if (alive && p.lse != nullptr && h == 0 && grow < p.Nq) {
+                // ln sum_k exp(scale * q.k): the kernel's row sum is 2688 * sum_k 2^((S_k - m) s) over the smoothed
+                // scores S (delta_s included); K smoothing took scale * q.km out of every score of the row
+                const float ms_fin = (m_run == -INFINITY ? 0.f : m_run) * sl2;
+                const float scale = p.sm_scale_per_head ? p.sm_scale_per_head[hq] : p.sm_scale;
+                const float v = (ms_fin + __log2f(l_tot) + kPScaleLog2) * 0.6931471805599453f +
+                                scale * p.qkm[(size_t)bhq * p.nqt * kBlock + grow];
+                p.lse[(size_t)bhq * p.Nq + grow] = (l_tot == 0.f) ? -INFINITY : v;
+            }
             if (alive) {
                 const float inv_l = (l_tot == 0.f || l_tot != l_tot) ? 0.f : __frcp_rn(l_tot);
                 OutT* orow = static_cast<OutT*>(p.out) + b * p.os0 + hq * p.os1 + (int64_t)grow * p.os2 + (D / 2) * h;
@@ -615,6 +627,7 @@ cudaError_t launch_attn(const AttnArgs& a, cudaStream_t st, int* driver_rc) {
     p.q_sf = a.q_sf; p.k_sf = a.k_sf; p.v_sf = a.v_sf;
     p.delta = static_cast<const uint16_t*>(a.delta);
     p.out = a.out;
+    p.lse = a.lse; p.qkm = a.qkm; p.sm_scale = a.sm_scale;
     p.os0 = a.os[0]; p.os1 = a.os[1]; p.os2 = a.os[2];
     p.status = a.status;
     p.debug = a.debug;

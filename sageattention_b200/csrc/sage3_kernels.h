@@ -17,6 +17,7 @@ struct PrepassArgs {
     float* kpart;
     void *km, *qm, *delta;
     uint8_t *q_codes, *q_sf, *k_codes, *k_sf, *v_codes, *v_sf;
+    float* qkm;                    // fp32 [B][Hq][Nq_p]: q . km per query row
     int* status;                   // device status words (bounded waits report here)
 };
 
@@ -29,6 +30,8 @@ struct AttnArgs {
     const uint8_t *q_codes, *q_sf, *k_codes, *k_sf, *v_codes, *v_sf;
     void* out;
     int64_t os[3];
+    float* lse;                     // optional fp32 [B][Hq][Nq]; nullptr if not wanted
+    const float* qkm;               // fp32 [B][Hq][Nq_p] from the pre-pass
     int* status;
     float* debug;                   // optional diagnostics dump of the first CTA; nullptr in normal use
 };

@@ -133,7 +133,10 @@ __global__ void __launch_bounds__(256, 3) quant_rows_kernel(
     const T* __restrict__ mean_in,     // one mean per head: qm [B*H][D]; unused for block mean
     T* __restrict__ qm_out,            // block mean: [B*H][Np/128][D]
     uint8_t* __restrict__ codes,       // [B*H][Np][D/2]
-    uint8_t* __restrict__ sfs) {       // [B*H][Np/128][D/64][512]
+    uint8_t* __restrict__ sfs,         // [B*H][Np/128][D/64][512]
+    const T* __restrict__ km,          // K means [B*Hkv][D]
+    int group,                         // query heads per kv head
+    float* __restrict__ qkm) {         // [B*H][Np]: x . km per row (the score part that K smoothing removes)
     constexpr int CH = D / 16;            // microblocks per row
     constexpr int RPP = 256 / CH;         // rows per pass
     constexpr int ITEMS = kBlock / RPP;   // microblocks per thread
@@ -155,6 +158,26 @@ __global__ void __launch_bounds__(256, 3) quant_rows_kernel(
     for (int i = 0; i < ITEMS; ++i) {
         const int r = row0 + rl + RPP * i;
         load16_packed<T>(base + (int64_t)r * sn + c * 16, r < N, raw[i][0], raw[i][1]);
+    }
+
+    // x . km of every row: 16 products per thread, then a sum over the CH neighbouring lanes that share the row
+    {
+        const T* kmh = km + ((int64_t)b * (H / group) + h / group) * D + c * 16;
+        uint4 k0, k1;
+        load16_packed<T>(kmh, true, k0, k1);
+        float kf[16];
+        unpack16<T>(k0, k1, kf);
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            float f[16];
+            unpack16<T>(raw[i][0], raw[i][1], f);
+            float dot = 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) dot = fmaf(f[j], kf[j], dot);
+#pragma unroll
+            for (int off = 1; off < CH; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+            if (c == 0) qkm[(int64_t)bh * Np + row0 + rl + RPP * i] = dot;
+        }
     }
 
     if (MODE == kModeQBlockMean) {
@@ -473,7 +496,7 @@ static cudaError_t launch_prepass_t(const PrepassArgs& a, cudaStream_t st) {
     const size_t smem_q = D * 4 + (D / 64) * 512 + 8 * D * 4;
     if (a.per_block_mean) {
         quant_rows_kernel<T, D, kModeQBlockMean><<<dim3(a.Nq_p / kBlock, BHq), 256, smem_q, st>>>(
-            q, a.qs[0], a.qs[1], a.qs[2], a.Hq, a.Nq, a.Nq_p, nullptr, qm, a.q_codes, a.q_sf);
+            q, a.qs[0], a.qs[1], a.qs[2], a.Hq, a.Nq, a.Nq_p, nullptr, qm, a.q_codes, a.q_sf, km, a.Hq / a.Hkv, a.qkm);
     } else {
         // one mean per head over the padded rows (api.py:88-90); kpart is free again: the K finalize has
         // consumed it and stream order serializes the two uses
@@ -481,7 +504,7 @@ static cudaError_t launch_prepass_t(const PrepassArgs& a, cudaStream_t st) {
                                                                             a.kpart, a.kchunks_q);
         colmean_finalize_kernel<T, D><<<BHq, D, 0, st>>>(a.kpart, a.kchunks_q, 1.0f / (float)a.Nq_p, qm);
         quant_rows_kernel<T, D, kModeQGlobalMean><<<dim3(a.Nq_p / kBlock, BHq), 256, smem_q, st>>>(
-            q, a.qs[0], a.qs[1], a.qs[2], a.Hq, a.Nq, a.Nq_p, qm, nullptr, a.q_codes, a.q_sf);
+            q, a.qs[0], a.qs[1], a.qs[2], a.Hq, a.Nq, a.Nq_p, qm, nullptr, a.q_codes, a.q_sf, km, a.Hq / a.Hkv, a.qkm);
     }
     const size_t smem_k = 2 * (D / 64) * 16384 + D * 4 + (D / 64) * 512 + 64 + 1024;
     cudaError_t e = cudaFuncSetAttribute(quant_k_delta_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_k);

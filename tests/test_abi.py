@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
     lib = _cabi.lib()
     for name in declared:
         assert getattr(lib, name) is not None
-    assert lib.sage3_version() == 1
+    assert lib.sage3_version() == 2
 
 
 def test_strerror_is_total():
@@ -44,11 +44,12 @@ def test_workspace_layout_config1():
     w = _cabi.Sage3Workspace()
     assert lib.sage3_workspace_layout(C.byref(d), C.byref(w)) == 0
     assert (w.nq_pad, w.nk_pad, w.nqm, w.kchunks) == (1024, 1024, 8, 2)
-    offs = [w.status, w.kpart, w.km, w.qm, w.delta, w.q_codes, w.q_sf, w.k_codes, w.k_sf, w.v_codes, w.v_sf, w.total_bytes]
+    offs = [w.status, w.kpart, w.km, w.qm, w.delta, w.q_codes, w.q_sf, w.k_codes, w.k_sf, w.v_codes, w.v_sf, w.qkm, w.total_bytes]
     assert offs == sorted(offs) and all(o % 1024 == 0 for o in offs)
     assert w.q_sf - w.q_codes == 2 * 1024 * 64               # packed codes: D/2 bytes per row
     assert w.k_codes - w.q_sf == 2 * 8 * 2 * 512             # 2 heads x 8 tiles x 2 atoms x 512 bytes
-    assert w.total_bytes - w.v_sf == 2 * 8 * 1024
+    assert w.qkm - w.v_sf == 2 * 8 * 1024
+    assert w.total_bytes - w.qkm == 2 * 1024 * 4                  # one fp32 per (head, padded query row)
     assert lib.sage3_workspace_bytes(C.byref(d)) == w.total_bytes
 
 
@@ -91,5 +92,5 @@ def test_python_surface_rejects_cpu_tensors():
         sageattn3(q, q, q)
     with pytest.raises(NotImplementedError):
         sageattn3(q, q, q, attn_mask=torch.ones(1))
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(RuntimeError):
         sageattn3(q, q, q, return_lse=True)

@@ -123,3 +123,26 @@ def test_offload_matches_device_call(cuda_device, layout, causal):
         out = sageattn3_offload(qp, kp, vp, tensor_layout=layout, is_causal=causal, kv_heads_per_chunk=per_chunk)
         torch.cuda.synchronize()
         assert torch.equal(out, ref), per_chunk
+
+
+@pytest.mark.parametrize("case", [CASES[0], CASES[4], CASES[8], CASES[9]], ids=lambda c: c[0])
+def test_lse_matches_oracle(cuda_device, case):
+    """return_lse (sageattention/core.py:86, 327): ln sum_k exp(scale * q.k) per query row.  Against the oracle the
+    tolerance is that of log2 / exp2 approximations (1e-3 absolute); the distance to the fp32 value is printed."""
+    name, B, Hq, Hkv, Nq, Nk, D, dt, causal, layout, extra = case
+    q, k, v = O.make_inputs(B, Hq, Hkv, Nq, Nk, D, seed=7 + Nq, dtype=dt, **extra)
+    if layout == "NHD":
+        q, k, v = (t.transpose(1, 2).contiguous() for t in (q, k, v))
+    out, lse = sageattn(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), tensor_layout=layout, is_causal=causal,
+                        return_lse=True)
+    torch.cuda.synchronize()
+    ref_out, ref_lse = O.sageattn3_oracle(q, k, v, tensor_layout=layout, is_causal=causal, return_lse=True)
+    full = O.fp32_lse(q, k, tensor_layout=layout, is_causal=causal)
+    lse = lse.cpu()
+    assert lse.shape == (B, Hq, Nq) and lse.dtype == torch.float32
+    assert O.cosine(out.cpu(), ref_out) >= COS_MIN
+    dead = torch.isinf(ref_lse)
+    assert torch.equal(torch.isinf(lse), dead)                   # rows without a visible key: -inf in both
+    err = (lse - ref_lse)[~dead].abs().max().item()
+    print(f"{name}: lse vs oracle max abs {err:.2e} | vs fp32 max abs {(lse - full)[~dead].abs().max().item():.3f}")
+    assert err <= 1e-3

@@ -122,3 +122,12 @@ def test_golden_fixtures():
         pp = O.prepass(q, k, v, per_block_mean=case["per_block_mean"])
         assert torch.equal(O.pack_nibbles(pp.q_codes)[0, 0, :8], case["q_codes_head"])
         assert torch.equal(pp.k_sf[0, 0, :8], case["k_sf_head"])
+
+
+def test_lse_close_to_fp32():
+    """The oracle's log-sum-exp (quantized scores + sm_scale * q.km) tracks the fp32 value of the unquantized inputs."""
+    q, k, v = O.make_inputs(1, 4, 2, 300, 300, 64, seed=5, k_offset_std=1.0)
+    _, lse = O.sageattn3_oracle(q, k, v, is_causal=True, return_lse=True)
+    ref = O.fp32_lse(q, k, is_causal=True)
+    assert lse.shape == (1, 4, 300)
+    assert (lse - ref).abs().max() < 0.5 and (lse - ref).abs().mean() < 0.05
