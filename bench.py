@@ -165,7 +165,7 @@ def run_ulysses(args, w, q, k, v, flops, rank, world, local, dev):
     from sageattention_b200.ulysses import ulysses_attention
     stream = torch.cuda.current_stream()
     hkv_l = w["Hkv"] // world
-    groups = max(1, min(args.overlap_groups if args.overlap_groups else 3, hkv_l))      # ulysses_attention's own rule
+    groups = max(1, min(args.overlap_groups if args.overlap_groups else 1, hkv_l))      # ulysses_attention's own rule
     for _ in range(max(args.warmup, 3)):
         ulysses_attention(q, k, v, tensor_layout=w["layout"], overlap_groups=groups)
     sampler = ClockSampler(local)
@@ -211,7 +211,7 @@ def main():
     ap.add_argument("--ulysses", action="store_true",
                     help="strong scaling: the workload's tokens are sharded over the ranks (all-to-all before and after attention)")
     ap.add_argument("--overlap-groups", type=int, default=0,
-                    help="with --ulysses: head slices whose all-to-all overlaps the kernels of the others (0 = up to 3)")
+                    help="with --ulysses: head slices whose all-to-all overlaps the kernels of the others (0 = one slice, no overlap)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     if args.impl == "reference":

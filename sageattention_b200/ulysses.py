@@ -84,9 +84,10 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_
     sageattn3; the result equals attn_fn on the gathered tensors, bit for bit, because every head is
     computed by exactly one rank from exactly the same inputs.
 
-    The rank's heads are processed in `overlap_groups` slices (default: up to 3, whole kv heads each): the
+    With `overlap_groups` = G > 1 the rank's heads are processed in G slices (whole kv heads each): the
     all-to-all of slice g + 1 and the return all-to-all of slice g - 1 run on NCCL's stream while slice g is
-    in the pre-pass and attention kernels.
+    in the pre-pass and attention kernels.  The default is one slice: on NVSwitch the exchange is a few per cent
+    of a step, and at two GPUs three slices measured 3 % slower than one (more, smaller launches).
     """
     if attn_fn is None:
         from .api import sageattn3 as attn_fn
@@ -101,7 +102,7 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_
         raise ValueError(f"Ulysses needs the head counts ({Hq}, {Hkv}) to be multiples of the world size {world}")
     hq_l, hkv_l = Hq // world, Hkv // world          # heads this rank computes
     rep = hq_l // hkv_l
-    G = overlap_groups if overlap_groups is not None else min(3, hkv_l)
+    G = overlap_groups if overlap_groups is not None else 1
     G = max(1, min(G, hkv_l))
     bounds = [(g * hkv_l) // G for g in range(G + 1)]      # slices of the local kv heads
     q5, k5, v5 = (t.reshape(B, world, -1, n, D) for t in (qh, kh, vh))   # [B, dest rank, its heads, n, D]

@@ -103,7 +103,7 @@ def _worker_slices(rank, world, port, groups, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("groups", [None, 2, 7])
+@pytest.mark.parametrize("groups", [3, 2, 7])
 def test_head_slices_overlap_gives_the_same_result(groups):
     """Three kv heads (six q heads) per rank, processed in 3, 2 (uneven) and 3 (clamped) slices."""
     world = 2
