@@ -150,6 +150,16 @@ SAGE3_API int sage3_attn_fwd_debug(const Sage3Desc* desc, void* ws, void* out, f
 SAGE3_API int sage3_selftest_wait_timeout(void* ws, void* stream);
 
 /*
+ * Strided copy of n0 x n1 x n2 contiguous slabs of `slab_bytes` bytes each: slab (i0, i1, i2) goes from
+ * src + i0*ss[0] + i1*ss[1] + i2*ss[2] to dst + i0*ds[0] + i1*ds[1] + i2*ds[2] (strides in bytes).  Everything
+ * (pointers, strides, slab_bytes) must be a multiple of 16.  This is the head <-> token regrouping around the two
+ * all-to-alls of sequence-parallel attention (a slab = the [tokens, D] block of one (batch, head)).  No counterpart in
+ * the reference, whose parallel example leaves the exchange to xfuser (example/parallel_sageattn_cogvideo.py:8-14).
+ */
+SAGE3_API int sage3_slab_copy(void* dst, const void* src, int32_t n0, int32_t n1, int32_t n2, const int64_t ds[3],
+                              const int64_t ss[3], int64_t slab_bytes, void* stream);
+
+/*
  * Mean of K over its Nk tokens, per (batch, kv-head) and channel -- the first stage of the pre-pass -- for
  * callers that must not allocate device memory and cannot hand over a workspace: for instance a serving
  * engine that gave all device memory to its own pool at start-up, or a latency-critical loop in which a

@@ -119,6 +119,31 @@ __global__ void wait_timeout_selftest_kernel(int* status) {
     sage3::mbar_wait(sage3::smem_u32(&bar), 0, &abort_flag, status, sage3::kWaitSelfTest, 2000000LL);
 }
 
+// Slab copy: blockIdx.y = slab, blockIdx.x = piece of the slab; 8 independent 16-byte loads per thread in flight.
+struct SlabCopyArgs {
+    int n1, n2;
+    long long ds0, ds1, ds2, ss0, ss1, ss2;   // in 16-byte units
+    long long slab_v;                          // 16-byte vectors per slab
+};
+__global__ void __launch_bounds__(256) slab_copy_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, SlabCopyArgs a) {
+    const int slab = blockIdx.y;
+    const int i2 = slab % a.n2, i1 = (slab / a.n2) % a.n1, i0 = slab / (a.n2 * a.n1);
+    const uint4* s = src + i0 * a.ss0 + i1 * a.ss1 + i2 * a.ss2;
+    uint4* d = dst + i0 * a.ds0 + i1 * a.ds1 + i2 * a.ds2;
+    const long long base = (long long)blockIdx.x * (256 * 8) + threadIdx.x;
+    uint4 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const long long idx = base + i * 256;
+        if (idx < a.slab_v) v[i] = __ldg(s + idx);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const long long idx = base + i * 256;
+        if (idx < a.slab_v) d[idx] = v[i];
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -203,6 +228,26 @@ SAGE3_API int sage3_selftest_wait_timeout(void* ws, void* stream) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (cudaMemsetAsync(ws, 0, 64 * sizeof(int32_t), st) != cudaSuccess) return SAGE3_E_CUDA;
     wait_timeout_selftest_kernel<<<1, 32, 0, st>>>(static_cast<int*>(ws));
+    return cudaGetLastError() == cudaSuccess ? SAGE3_OK : SAGE3_E_CUDA;
+}
+
+SAGE3_API int sage3_slab_copy(void* dst, const void* src, int32_t n0, int32_t n1, int32_t n2, const int64_t ds[3],
+                              const int64_t ss[3], int64_t slab_bytes, void* stream) {
+    if (!dst || !src || !ds || !ss) return SAGE3_E_NULL;
+    if (n0 <= 0 || n1 <= 0 || n2 <= 0 || slab_bytes <= 0) return SAGE3_E_SHAPE;
+    if ((int64_t)n0 * n1 * n2 > 65535) return SAGE3_E_TOO_LARGE;
+    if (!aligned(dst, 16) || !aligned(src, 16) || slab_bytes % 16) return SAGE3_E_ALIGN;
+    for (int i = 0; i < 3; ++i)
+        if (ds[i] % 16 || ss[i] % 16) return SAGE3_E_STRIDE;
+    SlabCopyArgs a;
+    a.n1 = n1; a.n2 = n2;
+    a.ds0 = ds[0] / 16; a.ds1 = ds[1] / 16; a.ds2 = ds[2] / 16;
+    a.ss0 = ss[0] / 16; a.ss1 = ss[1] / 16; a.ss2 = ss[2] / 16;
+    a.slab_v = slab_bytes / 16;
+    const long long pieces = (a.slab_v + 256 * 8 - 1) / (256 * 8);
+    if (pieces > 0x7fffffffLL) return SAGE3_E_TOO_LARGE;
+    slab_copy_kernel<<<dim3((unsigned)pieces, (unsigned)(n0 * n1 * n2)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint4*>(dst), static_cast<const uint4*>(src), a);
     return cudaGetLastError() == cudaSuccess ? SAGE3_OK : SAGE3_E_CUDA;
 }
 
