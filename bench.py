@@ -162,7 +162,9 @@ def run_ulysses(args, w, q, k, v, flops, rank, world, local, dev):
     """Strong-scaling arm: one step = all-to-all, pre-pass, attention, all-to-all on every rank."""
     import torch
     import torch.distributed as dist
-    from sageattention_b200.ulysses import ulysses_attention
+    from sageattention_b200.ulysses import ring_attention, ulysses_attention
+    if args.ring:        # same token shards, K / V shards travel around the ring instead of the two all-to-alls
+        ulysses_attention = lambda q_, k_, v_, tensor_layout, overlap_groups: ring_attention(q_, k_, v_, tensor_layout=tensor_layout)
     stream = torch.cuda.current_stream()
     hkv_l = w["Hkv"] // world
     groups = max(1, min(args.overlap_groups if args.overlap_groups else 1, hkv_l))      # ulysses_attention's own rule
@@ -190,11 +192,12 @@ def run_ulysses(args, w, q, k, v, flops, rank, world, local, dev):
             metric="attention TOPS (4*B*H*Nq*Nk*D/t) of the smooth+NVFP4-quantize+attend path", value=flops / (ms * 1e-3) / 1e12, unit="TOPS",
             n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=ms, higher_is_better=True, scaling="strong",
             vs_baseline=None, dtype="fp4 (e2m1 x ue4m3), fp32 accumulate", data="synthetic",
-            config=dict(workload=args.workload, sharding="ulysses sequence parallel: NCCL all-to-all before and after attention",
+            config=dict(workload=args.workload, sharding=("ring attention: K/V shards sent around the ring (NCCL send/recv), partial results merged by LSE"
+                                                          if args.ring else "ulysses sequence parallel: NCCL all-to-all before and after attention"),
                         tokens_per_rank=q.shape[2] if w["layout"] == "HND" else q.shape[1], heads_per_rank=w["Hq"] // world,
                         all_to_all_bytes_per_rank_per_step=per_rank_bytes, head_slices_in_flight=groups,
                         l2="inputs larger than L2"),
-            clocks=clocks, gpu_launches=6 * groups * args.steps)))
+            clocks=clocks, gpu_launches=((6 + 1) * world if args.ring else 6 * groups + 4) * args.steps)))
     dist.destroy_process_group()
 
 
@@ -210,6 +213,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ulysses", action="store_true",
                     help="strong scaling: the workload's tokens are sharded over the ranks (all-to-all before and after attention)")
+    ap.add_argument("--ring", action="store_true", help="with --ulysses: ring attention instead of the all-to-all exchange")
     ap.add_argument("--overlap-groups", type=int, default=0,
                     help="with --ulysses: head slices whose all-to-all overlaps the kernels of the others (0 = one slice, no overlap)")
     args = ap.parse_args()

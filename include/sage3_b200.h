@@ -160,6 +160,18 @@ SAGE3_API int sage3_slab_copy(void* dst, const void* src, int32_t n0, int32_t n1
                               const int64_t ss[3], int64_t slab_bytes, void* stream);
 
 /*
+ * Merges one partial attention result into a running one (context-parallel / ring composition of attention over
+ * disjoint key sets, the use `return_lse` exists for: sageattention/core.py:120-122).  For every row r of `rows`:
+ *   lse' = log(exp(lse_acc[r]) + exp(lse_part[r]));  acc[r][:] = acc[r][:] * exp(lse_acc[r] - lse') +
+ *   o_part[r][:] * exp(lse_part[r] - lse');  lse_acc[r] = lse'.
+ * `acc` fp32 [rows][D] and `lse_acc` fp32 [rows] are read and written (ignored on input when first != 0);
+ * `o_part` is `dtype` [rows][D] contiguous, `lse_part` fp32 [rows]; when `out` is not NULL the merged rows are also
+ * written to it in `dtype` ([rows][D] contiguous).  D must be a multiple of 8.  No counterpart in the reference.
+ */
+SAGE3_API int sage3_merge_partial(float* acc, float* lse_acc, const void* o_part, const float* lse_part, void* out,
+                                  int64_t rows, int32_t D, int32_t dtype, int32_t first, void* stream);
+
+/*
  * Mean of K over its Nk tokens, per (batch, kv-head) and channel -- the first stage of the pre-pass -- for
  * callers that must not allocate device memory and cannot hand over a workspace: for instance a serving
  * engine that gave all device memory to its own pool at start-up, or a latency-critical loop in which a

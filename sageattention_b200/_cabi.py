@@ -72,6 +72,8 @@ def lib() -> C.CDLL:
     l.sage3_selftest_wait_timeout.argtypes = [V, V]
     l.sage3_slab_copy.restype = C.c_int
     l.sage3_slab_copy.argtypes = [V, V, C.c_int32, C.c_int32, C.c_int32, P(C.c_int64 * 3), P(C.c_int64 * 3), C.c_int64, V]
+    l.sage3_merge_partial.restype = C.c_int
+    l.sage3_merge_partial.argtypes = [V, V, V, V, V, C.c_int64, C.c_int32, C.c_int32, C.c_int32, V]
     l.sage3_kmean_noalloc.restype = C.c_int
     l.sage3_kmean_noalloc.argtypes = [P(Sage3Desc), V, V, V]
     l.sage3_check_status.restype = C.c_int
@@ -81,7 +83,7 @@ def lib() -> C.CDLL:
 
 
 EXPORTED = ["sage3_version", "sage3_strerror", "sage3_workspace_layout", "sage3_workspace_bytes", "sage3_prepass",
-            "sage3_attn_fwd", "sage3_fwd", "sage3_check_status", "sage3_attn_fwd_debug", "sage3_kmean_noalloc", "sage3_selftest_wait_timeout", "sage3_slab_copy"]
+            "sage3_attn_fwd", "sage3_fwd", "sage3_check_status", "sage3_attn_fwd_debug", "sage3_kmean_noalloc", "sage3_selftest_wait_timeout", "sage3_slab_copy", "sage3_merge_partial"]
 
 
 def check(code: int, where: str) -> None:

@@ -144,6 +144,51 @@ __global__ void __launch_bounds__(256) slab_copy_kernel(uint4* __restrict__ dst,
     }
 }
 
+// Merge of a partial attention result into the running one: 8 channels per thread.
+template <typename T>
+__global__ void __launch_bounds__(256) merge_partial_kernel(float* __restrict__ acc, float* __restrict__ lse_acc,
+                                                            const T* __restrict__ o_part, const float* __restrict__ lse_part,
+                                                            T* __restrict__ out, long long rows, int D, int first) {
+    const int tpr = D / 8;                                   // threads per row
+    const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;
+    const long long r = idx / tpr;
+    const int c = (int)(idx % tpr) * 8;
+    if (r >= rows) return;
+    const float lp = lse_part[r];
+    const float la = first ? -INFINITY : lse_acc[r];
+    const float mx = fmaxf(la, lp);
+    float ln = mx, wa = 0.f, wp = 0.f;
+    if (mx != -INFINITY) {
+        const float ea = __expf(la - mx), ep = __expf(lp - mx);
+        ln = mx + __logf(ea + ep);
+        wa = __expf(la - ln);
+        wp = __expf(lp - ln);
+    }
+    const uint4 raw = *reinterpret_cast<const uint4*>(o_part + r * D + c);
+    const T* ov = reinterpret_cast<const T*>(&raw);
+    float a[8];
+    if (first) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i] = 0.f;
+    } else {
+        const float4 a0 = *reinterpret_cast<const float4*>(acc + r * D + c), a1 = *reinterpret_cast<const float4*>(acc + r * D + c + 4);
+        a[0] = a0.x; a[1] = a0.y; a[2] = a0.z; a[3] = a0.w; a[4] = a1.x; a[5] = a1.y; a[6] = a1.z; a[7] = a1.w;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a[i] = a[i] * wa + static_cast<float>(ov[i]) * wp;
+    *reinterpret_cast<float4*>(acc + r * D + c) = make_float4(a[0], a[1], a[2], a[3]);
+    *reinterpret_cast<float4*>(acc + r * D + c + 4) = make_float4(a[4], a[5], a[6], a[7]);
+    if (out != nullptr) {
+        uint4 w;
+        T* wv = reinterpret_cast<T*>(&w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) wv[i] = static_cast<T>(a[i]);
+        *reinterpret_cast<uint4*>(out + r * D + c) = w;
+    }
+    __syncwarp();
+    if (c == 0) lse_acc[r] = ln;       // (every thread of the row has read lse_acc above: rows never straddle warps, D/8 divides 32)
+}
+
 }  // namespace
 
 extern "C" {
@@ -248,6 +293,25 @@ SAGE3_API int sage3_slab_copy(void* dst, const void* src, int32_t n0, int32_t n1
     if (pieces > 0x7fffffffLL) return SAGE3_E_TOO_LARGE;
     slab_copy_kernel<<<dim3((unsigned)pieces, (unsigned)(n0 * n1 * n2)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<uint4*>(dst), static_cast<const uint4*>(src), a);
+    return cudaGetLastError() == cudaSuccess ? SAGE3_OK : SAGE3_E_CUDA;
+}
+
+SAGE3_API int sage3_merge_partial(float* acc, float* lse_acc, const void* o_part, const float* lse_part, void* out,
+                                  int64_t rows, int32_t D, int32_t dtype, int32_t first, void* stream) {
+    if (!acc || !lse_acc || !o_part || !lse_part) return SAGE3_E_NULL;
+    if (rows <= 0 || D <= 0 || D % 8 != 0 || (256 % (D / 8)) != 0 || (32 % (D / 8)) != 0) return SAGE3_E_SHAPE;
+    if (dtype != SAGE3_FP16 && dtype != SAGE3_BF16) return SAGE3_E_DTYPE;
+    if (!aligned(acc, 16) || !aligned(o_part, 16) || (out && !aligned(out, 16))) return SAGE3_E_ALIGN;
+    const long long threads = (long long)rows * (D / 8);
+    const long long blocks = (threads + 255) / 256;
+    if (blocks > 0x7fffffffLL) return SAGE3_E_TOO_LARGE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == SAGE3_BF16)
+        merge_partial_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(acc, lse_acc, static_cast<const __nv_bfloat16*>(o_part),
+                                                                             lse_part, static_cast<__nv_bfloat16*>(out), rows, D, first);
+    else
+        merge_partial_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(acc, lse_acc, static_cast<const __half*>(o_part), lse_part,
+                                                                     static_cast<__half*>(out), rows, D, first);
     return cudaGetLastError() == cudaSuccess ? SAGE3_OK : SAGE3_E_CUDA;
 }
 

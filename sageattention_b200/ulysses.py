@@ -10,6 +10,11 @@ Two schemes, as the reference's parallel example uses them through xfuser
   quantization need the whole sequence of a head, so they run after the exchange), a second all-to-all
   returns the output to token shards (`ulysses_attention`).
 
+For head counts smaller than (or not divisible by) the number of GPUs there is ring attention on the same token
+shards (`ring_attention`): K / V shards travel around the ring while every rank attends its queries to the shard it
+holds, and the partial results are merged through their log-sum-exp (the use `return_lse` exists for,
+sageattention/core.py:120-122).
+
 The exchanged tensors land in this GPU's own memory before any kernel reads them.
 """
 from __future__ import annotations
@@ -163,3 +168,78 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_
         _regroup(out5[:, :, a * rep:b_ * rep], recv_o.permute(1, 0, 2, 3, 4))     # [B, source rank, its slice of heads, n, D]
     o = out5.reshape(B, Hq, n, D)
     return o if tensor_layout == "HND" else o.transpose(1, 2)
+
+
+# ------------------------------------------------------------------------------------------------------
+# ring attention (context parallel): merges partial results over disjoint key shards through their LSE
+# ------------------------------------------------------------------------------------------------------
+def merge_partial(acc: torch.Tensor | None, lse_acc: torch.Tensor | None, o_part: torch.Tensor, lse_part: torch.Tensor,
+                  want_out: bool):
+    """Folds (o_part [.., n, D] in 16-bit, lse_part [.., n] fp32) into the running (acc fp32, lse_acc).  Returns
+    (acc, lse_acc, out) where out is the merged result in o_part's dtype when `want_out`, else None.
+    On the GPU this is one launch of the library's merge kernel; host tensors (the gloo tests) use tensor
+    expressions of the same formula."""
+    first = acc is None
+    D = o_part.shape[-1]
+    if o_part.is_cuda:
+        import ctypes as C
+        from . import _cabi
+        o_part = o_part.contiguous()
+        lse_part = lse_part.contiguous()
+        if first:
+            acc = torch.empty(o_part.shape, dtype=torch.float32, device=o_part.device)
+            lse_acc = torch.empty(lse_part.shape, dtype=torch.float32, device=o_part.device)
+        out = torch.empty_like(o_part) if want_out else None
+        dt = {torch.float16: _cabi.SAGE3_FP16, torch.bfloat16: _cabi.SAGE3_BF16}[o_part.dtype]
+        with torch.cuda.device(o_part.device):
+            _cabi.check(_cabi.lib().sage3_merge_partial(
+                acc.data_ptr(), lse_acc.data_ptr(), o_part.data_ptr(), lse_part.data_ptr(),
+                None if out is None else out.data_ptr(), o_part.numel() // D, D, dt, int(first),
+                torch.cuda.current_stream(o_part.device).cuda_stream), "sage3_merge_partial")
+        return acc, lse_acc, out
+    la = torch.full_like(lse_part, -float("inf")) if first else lse_acc
+    mx = torch.maximum(la, lse_part)
+    dead = torch.isinf(mx) & (mx < 0)
+    mz = torch.where(dead, torch.zeros_like(mx), mx)
+    ln = torch.where(dead, mx, mz + torch.log(torch.exp(la - mz) + torch.exp(lse_part - mz)))
+    wa = torch.where(dead, torch.zeros_like(mx), torch.exp(la - torch.where(dead, torch.zeros_like(ln), ln)))
+    wp = torch.where(dead, torch.zeros_like(mx), torch.exp(lse_part - torch.where(dead, torch.zeros_like(ln), ln)))
+    base = torch.zeros(o_part.shape, dtype=torch.float32) if first else acc
+    acc = base * wa.unsqueeze(-1) + o_part.to(torch.float32) * wp.unsqueeze(-1)
+    return acc, ln, (acc.to(o_part.dtype) if want_out else None)
+
+
+def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
+                   group: dist.ProcessGroup | None = None, attn_fn: Callable | None = None, **kwargs):
+    """Context-parallel attention without a head-count condition.  Every rank passes its contiguous token shard
+    of all heads (q [B,Hq,N/P,D], k, v [B,Hkv,N/P,D] for "HND") and gets the output for the same shard.
+
+    P steps: the rank attends its queries to the K / V shard it currently holds
+    (`attn_fn(q, k, v, tensor_layout="HND", return_lse=True, **kwargs)` -> (o, lse), default sageattn3) while that
+    shard is sent on to the next rank and the next one arrives from the previous rank; the P partial results are
+    merged through their log-sum-exp.  Smoothing and quantization are per shard (every partial call is a complete
+    attention over its own keys), so the result agrees with the single-GPU call to within the FP4 noise of the
+    method, not bit for bit.  Non-causal only."""
+    if kwargs.get("is_causal"):
+        raise NotImplementedError("ring_attention is non-causal (the shards would need per-step masks)")
+    if attn_fn is None:
+        from .api import sageattn3 as attn_fn
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    qh, kh, vh = (_to_hnd(t, tensor_layout).contiguous() for t in (q, k, v))
+    kv = torch.stack((kh, vh))                      # one buffer per hop
+    nxt = dist.get_global_rank(group, (rank + 1) % world) if group is not None else (rank + 1) % world
+    prv = dist.get_global_rank(group, (rank - 1) % world) if group is not None else (rank - 1) % world
+    acc = lse_acc = out = None
+    for step in range(world):
+        reqs, kv_next = [], None
+        if step + 1 < world:
+            kv_next = torch.empty_like(kv)
+            reqs = dist.batch_isend_irecv([dist.P2POp(dist.isend, kv, nxt, group), dist.P2POp(dist.irecv, kv_next, prv, group)])
+        o, lse = attn_fn(qh, kv[0], kv[1], tensor_layout="HND", return_lse=True, **kwargs)
+        acc, lse_acc, out = merge_partial(acc, lse_acc, o, lse, want_out=(step + 1 == world))
+        for r in reqs:
+            r.wait()
+        if kv_next is not None:
+            kv = kv_next
+    return out if tensor_layout == "HND" else out.transpose(1, 2)

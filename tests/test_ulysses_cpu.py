@@ -111,3 +111,52 @@ def test_head_slices_overlap_gives_the_same_result(groups):
         ret = mgr.dict()
         mp.spawn(_worker_slices, args=(world, _free_port(), groups, ret), nprocs=world, join=True)
         assert dict(ret) == {0: True, 1: True}
+
+
+def _worker_ring(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        q, k, v = O.make_inputs(1, 3, 3, 384, 384, 64, seed=79, k_offset_std=1.0)     # 3 heads: Ulysses could not split them
+        n = 384 // world
+        cut = lambda x: x[:, :, rank * n:(rank + 1) * n]
+        out = U.ring_attention(cut(q), cut(k), cut(v), attn_fn=O.sageattn3_oracle)
+        # the same composition in one process: this rank's queries against every key shard, merged in ring order
+        acc = lse = exp = None
+        for step in range(world):
+            j = (rank - step) % world
+            o_j, l_j = O.sageattn3_oracle(cut(q), k[:, :, j * n:(j + 1) * n], v[:, :, j * n:(j + 1) * n], return_lse=True)
+            acc, lse, exp = U.merge_partial(acc, lse, o_j, l_j, want_out=(step + 1 == world))
+        full = O.fp32_attention(q, k, v)
+        ret[rank] = (bool(torch.equal(out, exp)), O.cosine(out, cut(full)), O.rel_l1(out, cut(full)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ring_attention_over_gloo():
+    """Three heads on two ranks (not divisible: the case ring attention exists for).  The distributed result equals the
+    single-process composition bit for bit, and sits at the method's usual distance from fp32 attention."""
+    world = 2
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker_ring, args=(world, _free_port(), ret), nprocs=world, join=True)
+        for r in range(world):
+            same, cos, l1 = ret[r]
+            assert same and cos > 0.97 and l1 < 0.3, (r, same, cos, l1)
+
+
+def test_merge_partial_is_softmax_composition():
+    """Merging attention over two disjoint key sets through their LSE equals attention over the union (fp32 check)."""
+    g = torch.Generator().manual_seed(4)
+    q = torch.randn(1, 2, 16, 32, generator=g)
+    k = torch.randn(1, 2, 48, 32, generator=g)
+    v = torch.randn(1, 2, 48, 32, generator=g)
+    def part(ks):
+        s = torch.matmul(q, k[:, :, ks].transpose(-1, -2)) * 32 ** -0.5
+        return torch.matmul(torch.softmax(s, -1), v[:, :, ks]).to(torch.bfloat16), torch.logsumexp(s, -1)
+    acc = lse = out = None
+    for ks in (slice(0, 16), slice(16, 48)):
+        o, l = part(ks)
+        acc, lse, out = U.merge_partial(acc, lse, o, l, want_out=True)
+    ref, ref_lse = part(slice(0, 48))
+    assert torch.allclose(out.float(), ref.float(), atol=2e-2) and torch.allclose(lse, ref_lse, atol=1e-5)
