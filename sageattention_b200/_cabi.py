@@ -12,6 +12,7 @@ _PKG = pathlib.Path(__file__).resolve().parent
 LIB_PATH = _PKG / "libsage3_b200.so"
 
 SAGE3_FP16, SAGE3_BF16 = 0, 1
+ABI_VERSION = 2          # SAGE3_ABI_VERSION of include/sage3_b200.h this module's structs were written for
 SAGE3_OK = 0
 SAGE3_E_DEVICE_WAIT = -9
 DEBUG_FLOATS = 33280
@@ -51,6 +52,10 @@ def lib() -> C.CDLL:
             f"{LIB_PATH} is missing; build it with `python -m sageattention_b200.build` "
             "(needs nvcc with sm_100a support). sageattention_b200 has no fallback path.")
     l = C.CDLL(str(LIB_PATH))
+    l.sage3_version.restype = C.c_int
+    if l.sage3_version() != ABI_VERSION:
+        raise ImportError(f"{LIB_PATH} has ABI version {l.sage3_version()}, this package needs {ABI_VERSION}: rebuild it "
+                          "with `python -m sageattention_b200.build`")
     P, V = C.POINTER, C.c_void_p
     l.sage3_version.restype = C.c_int
     l.sage3_version.argtypes = []
