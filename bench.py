@@ -209,7 +209,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="c2_hd128_32k", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="sage3_b200", choices=["sage3_b200", "reference"])
-    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--e2e-steps", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ulysses", action="store_true",
                     help="strong scaling: the workload's tokens are sharded over the ranks (all-to-all before and after attention)")
@@ -330,7 +330,8 @@ def main():
             # over (batch, kv-head) chunks
             sageattn3_offload(qh, kh, vh, out=oh, tensor_layout=w["layout"], is_causal=w["causal"], device=dev)
 
-        e2e_step()
+        for _ in range(3):          # warm-up: allocator, pinned pages, clocks
+            e2e_step()
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
