@@ -224,7 +224,6 @@ def main():
 
     import torch
     import torch.distributed as dist
-    from oracle import sage3_oracle as O            # input generator + the cpu_baseline leg only
     from sageattention_b200 import Sage3Problem, sageattn3_offload
 
     rank = int(os.environ.get("RANK", "0"))
