@@ -146,3 +146,13 @@ def test_lse_matches_oracle(cuda_device, case):
     err = (lse - ref_lse)[~dead].abs().max().item()
     print(f"{name}: lse vs oracle max abs {err:.2e} | vs fp32 max abs {(lse - full)[~dead].abs().max().item():.3f}")
     assert err <= 1e-3
+
+
+def test_lse_with_per_head_scale_and_global_mean(cuda_device):
+    q, k, v = O.make_inputs(1, 4, 2, 200, 330, 64, seed=12, dtype=torch.float16, k_offset_std=2.0)
+    scale = torch.tensor([0.05, 0.1, 0.125, 0.2])
+    out, lse = sageattn3(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), sm_scale=scale, per_block_mean=False,
+                         return_lse=True)
+    torch.cuda.synchronize()
+    ref_out, ref_lse = O.sageattn3_oracle(q, k, v, sm_scale=scale, per_block_mean=False, return_lse=True)
+    assert O.cosine(out.cpu(), ref_out) >= COS_MIN and (lse.cpu() - ref_lse).abs().max() <= 1e-3

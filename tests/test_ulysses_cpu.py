@@ -160,3 +160,8 @@ def test_merge_partial_is_softmax_composition():
         acc, lse, out = U.merge_partial(acc, lse, o, l, want_out=True)
     ref, ref_lse = part(slice(0, 48))
     assert torch.allclose(out.float(), ref.float(), atol=2e-2) and torch.allclose(lse, ref_lse, atol=1e-5)
+
+
+def test_ring_attention_is_non_causal_only():
+    with pytest.raises(NotImplementedError):
+        U.ring_attention(torch.zeros(1, 1, 8, 16), torch.zeros(1, 1, 8, 16), torch.zeros(1, 1, 8, 16), is_causal=True)
