@@ -4,6 +4,7 @@ Keeps the keyword surface of
   sageattn3_blackwell(q, k, v, attn_mask=None, is_causal=False, per_block_mean=True, **kwargs)
       (reference: sageattention3_blackwell/sageattn3/api.py:131-152)
   sageattn(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, return_lse=False, **kwargs)
+  sageattn_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, is_causal=False, sm_scale=None, **kwargs)
       (reference: sageattention/core.py:79-157)
 so the function can be patched over F.scaled_dot_product_attention or called from an attention
 processor exactly like the reference's.  Differences, all deliberate:
@@ -195,6 +196,34 @@ def sageattn(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, retur
     """Signature of the reference's v2 dispatcher (core.py:79-88); on B200 it always runs the FP4 path."""
     return sageattn3(q, k, v, tensor_layout=tensor_layout, is_causal=is_causal, sm_scale=sm_scale,
                      return_lse=return_lse, **kwargs)
+
+
+def sageattn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q, cu_seqlens_k,
+                    max_seqlen_q: int | None = None, max_seqlen_k: int | None = None, is_causal: bool = False,
+                    sm_scale=None, **kwargs) -> torch.Tensor:
+    """Signature of the reference's packed variable-length entry (sageattention/core.py:334-345): q
+    [total_q, Hq, D], k, v [total_k, Hkv, D]; sequence i owns rows cu_seqlens[i]:cu_seqlens[i+1].  Returns
+    [total_q, Hq, D].  Smoothing means are per sequence, so every sequence is one call of the FP4 path on its slice
+    (addressed through strides, nothing is copied); `max_seqlen_*` and `smooth_k` are accepted for compatibility."""
+    if q.dim() != 3 or k.dim() != 3 or v.dim() != 3:
+        raise ValueError("q, k, v must be packed as [tokens, heads, head_dim]")
+    cq = [int(x) for x in (cu_seqlens_q.tolist() if isinstance(cu_seqlens_q, torch.Tensor) else cu_seqlens_q)]
+    ck = [int(x) for x in (cu_seqlens_k.tolist() if isinstance(cu_seqlens_k, torch.Tensor) else cu_seqlens_k)]
+    if len(cq) != len(ck) or len(cq) < 2 or cq[0] != 0 or ck[0] != 0 or cq[-1] != q.shape[0] or ck[-1] != k.shape[0]:
+        raise ValueError("cu_seqlens_q / cu_seqlens_k must start at 0, end at the token counts and have equal length")
+    kwargs.pop("smooth_k", None)
+    out = torch.empty_like(q)
+    for i in range(len(cq) - 1):
+        q0, q1, k0, k1 = cq[i], cq[i + 1], ck[i], ck[i + 1]
+        if q1 == q0:
+            continue
+        if k1 == k0:
+            out[q0:q1].zero_()
+            continue
+        prob = Sage3Problem(q[q0:q1].unsqueeze(0), k[k0:k1].unsqueeze(0), v[k0:k1].unsqueeze(0), "NHD", is_causal, sm_scale,
+                            kwargs.get("per_block_mean", True), out=out[q0:q1].unsqueeze(0))
+        prob.run()
+    return out
 
 
 def sageattn3_offload(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor | None = None,

@@ -5,7 +5,7 @@ import pytest
 import torch
 
 from oracle import sage3_oracle as O
-from sageattention_b200 import Sage3Problem, sageattn, sageattn3, sageattn3_blackwell
+from sageattention_b200 import Sage3Problem, sageattn, sageattn3, sageattn3_blackwell, sageattn_varlen
 
 pytestmark = pytest.mark.gpu
 
@@ -156,3 +156,24 @@ def test_lse_with_per_head_scale_and_global_mean(cuda_device):
     torch.cuda.synchronize()
     ref_out, ref_lse = O.sageattn3_oracle(q, k, v, sm_scale=scale, per_block_mean=False, return_lse=True)
     assert O.cosine(out.cpu(), ref_out) >= COS_MIN and (lse.cpu() - ref_lse).abs().max() <= 1e-3
+
+
+def test_varlen_matches_per_sequence_calls(cuda_device):
+    """Packed variable-length batch (sageattention/core.py:334-345): every sequence equals its own dense call."""
+    lens_q, lens_k = [200, 0, 384, 77], [200, 50, 500, 77]
+    cq = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32)
+    ck = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)), dtype=torch.int32)
+    g = torch.Generator().manual_seed(21)
+    q = torch.randn(int(cq[-1]), 4, 64, generator=g).to(torch.bfloat16).to(cuda_device)
+    k = (torch.randn(int(ck[-1]), 2, 64, generator=g) + 1.0).to(torch.bfloat16).to(cuda_device)
+    v = torch.randn(int(ck[-1]), 2, 64, generator=g).to(torch.bfloat16).to(cuda_device)
+    out = sageattn_varlen(q, k, v, cq.to(cuda_device), ck.to(cuda_device), max(lens_q), max(lens_k), is_causal=False, smooth_k=True)
+    assert out.shape == q.shape
+    for i in range(4):
+        a, b, c, d = int(cq[i]), int(cq[i + 1]), int(ck[i]), int(ck[i + 1])
+        if b == a:
+            continue
+        one = sageattn3(q[a:b].unsqueeze(0), k[c:d].unsqueeze(0), v[c:d].unsqueeze(0), tensor_layout="NHD")
+        assert torch.equal(out[a:b], one[0])
+        ref = O.sageattn3_oracle(q[a:b].unsqueeze(0).cpu(), k[c:d].unsqueeze(0).cpu(), v[c:d].unsqueeze(0).cpu(), tensor_layout="NHD")
+        assert O.cosine(out[a:b].cpu(), ref[0]) >= COS_MIN
