@@ -226,6 +226,22 @@ def sageattn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlen
     return out
 
 
+_OFFLOAD_STATE: dict = {}
+
+
+def _retire_offload_state(st) -> None:
+    """Work that may still use the buffers has been enqueued on the state's streams: wait for it before the
+    allocator may hand the memory to someone else."""
+    if st is not None:
+        for s_ in st["streams"]:
+            s_.synchronize()
+
+
+def sageattn3_offload_release() -> None:
+    """Drops the device buffers and streams that sageattn3_offload keeps between calls."""
+    _retire_offload_state(_OFFLOAD_STATE.pop("state", None))
+
+
 def sageattn3_offload(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor | None = None,
                       tensor_layout: str = "HND", is_causal: bool = False, sm_scale=None, per_block_mean: bool = True,
                       device: torch.device | str | None = None, kv_heads_per_chunk: int | None = None) -> torch.Tensor:
@@ -234,7 +250,8 @@ def sageattn3_offload(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: to
 
     (Batch, kv-head) groups are independent, so the call is pipelined over chunks of them on three streams:
     while one chunk is being computed, the next one is copied in and the previous result is copied out.  Device
-    memory holds two chunks at a time, so the host tensors may be larger than the GPU.  The caller's current
+    memory holds two chunks at a time, so the host tensors may be larger than the GPU; the chunk buffers and
+    streams are kept for the next call of the same shape (`sageattn3_offload_release()` drops them).  The caller's current
     stream orders the call as a whole (it is waited for at entry and waits for the last copy at exit; the host
     is not blocked).  A scalar or None `sm_scale` only.
     """
@@ -255,8 +272,9 @@ def sageattn3_offload(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: to
     elif out.shape != q.shape or out.dtype != q.dtype or out.is_cuda:
         raise ValueError("out must be a host tensor shaped and typed like q")
     if kv_heads_per_chunk is None:
-        # about 16 chunks in total, whole kv heads per chunk
-        kv_heads_per_chunk = max(1, (B * Hkv + 15) // 16)
+        # about 32 chunks in total, whole kv heads per chunk, equal chunks (a divisor of Hkv)
+        target = max(1, (B * Hkv + 31) // 32)
+        kv_heads_per_chunk = max(d_ for d_ in range(1, Hkv + 1) if Hkv % d_ == 0 and d_ <= max(target, 1))
     kv_heads_per_chunk = min(kv_heads_per_chunk, Hkv)
     chunks = [(b, h0, min(h0 + kv_heads_per_chunk, Hkv)) for b in range(B) for h0 in range(0, Hkv, kv_heads_per_chunk)]
 
@@ -264,14 +282,23 @@ def sageattn3_offload(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: to
         return t[b:b + 1, h0 * g:h1 * g] if tensor_layout == "HND" else t[b:b + 1, :, h0 * g:h1 * g]
 
     cur = torch.cuda.current_stream(dev)
-    s_in, s_comp, s_out = (torch.cuda.Stream(dev) for _ in range(3))
+    # Streams, device buffers and their events survive the call (one set per process, replaced when the shapes or
+    # options change): allocating two chunks' worth of operands and workspace anew on every call costs more than
+    # a chunk's copy.  `sageattn3_offload_release()` gives the memory back.
+    state_key = (dev.index, tuple(q.shape), tuple(k.shape), q.dtype, tensor_layout, bool(is_causal), sm_scale,
+                 bool(per_block_mean), kv_heads_per_chunk)
+    st = _OFFLOAD_STATE.get("state")
+    if st is None or st["key"] != state_key:
+        _retire_offload_state(st)
+        st = dict(key=state_key, streams=tuple(torch.cuda.Stream(dev) for _ in range(3)), bufs=[{}, {}],
+                  comp_done=[None, None], out_done=[None, None])
+        _OFFLOAD_STATE["state"] = st
+    s_in, s_comp, s_out = st["streams"]
     start = torch.cuda.Event()
     start.record(cur)
     for s_ in (s_in, s_comp, s_out):
         s_.wait_event(start)
-    bufs = [None, None]          # per slot: (shape key, q_dev, k_dev, v_dev, problem)
-    comp_done = [None, None]
-    out_done = [None, None]
+    bufs, comp_done, out_done = st["bufs"], st["comp_done"], st["out_done"]     # per slot; carried over between calls
     for i, (b, h0, h1) in enumerate(chunks):
         slot = i & 1
         qh, kh, vh = cut(q, b, h0, h1, group), cut(k, b, h0, h1), cut(v, b, h0, h1)
@@ -279,16 +306,13 @@ def sageattn3_offload(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: to
         with torch.cuda.stream(s_in):
             if comp_done[slot] is not None:
                 s_in.wait_event(comp_done[slot])            # the chunk that used these buffers has been computed
-            if bufs[slot] is None or bufs[slot][0] != key:
+            if key not in bufs[slot]:                       # one set per chunk shape (a ragged last chunk has its own)
                 qd = torch.empty(qh.shape, dtype=q.dtype, device=dev)
                 kd = torch.empty(kh.shape, dtype=q.dtype, device=dev)
                 vd = torch.empty(vh.shape, dtype=q.dtype, device=dev)
                 prob = Sage3Problem(qd, kd, vd, tensor_layout, is_causal, sm_scale, per_block_mean)
-                for t_ in (qd, kd, vd, prob.out, prob.ws.buf):
-                    t_.record_stream(s_comp)
-                    t_.record_stream(s_out)
-                bufs[slot] = (key, qd, kd, vd, prob)
-            _, qd, kd, vd, prob = bufs[slot]
+                bufs[slot][key] = (qd, kd, vd, prob)        # kept alive by the state, ordered by the events below
+            qd, kd, vd, prob = bufs[slot][key]
             qd.copy_(qh, non_blocking=True)
             kd.copy_(kh, non_blocking=True)
             vd.copy_(vh, non_blocking=True)
