@@ -177,3 +177,22 @@ def test_varlen_matches_per_sequence_calls(cuda_device):
         assert torch.equal(out[a:b], one[0])
         ref = O.sageattn3_oracle(q[a:b].unsqueeze(0).cpu(), k[c:d].unsqueeze(0).cpu(), v[c:d].unsqueeze(0).cpu(), tensor_layout="NHD")
         assert O.cosine(out[a:b].cpu(), ref[0]) >= COS_MIN
+
+
+def test_cuda_graph_capture_and_replay(cuda_device):
+    """The whole call is a fixed sequence of launches on the caller's stream (no allocation, no synchronization), so it
+    can be captured once and replayed: the replay on new input values equals the eager call."""
+    q, k, v = (t.to(cuda_device) for t in O.make_inputs(1, 2, 2, 512, 512, 128, seed=3, k_offset_std=1.0))
+    prob = Sage3Problem(q.clone(), k.clone(), v.clone(), return_lse=True)
+    prob.run()                                   # warm-up outside the capture (function attributes, tensor-map entry point)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        prob.run()
+    q2, k2, v2 = (t.to(cuda_device) for t in O.make_inputs(1, 2, 2, 512, 512, 128, seed=4, k_offset_std=2.0))
+    prob.q.copy_(q2); prob.k.copy_(k2); prob.v.copy_(v2)
+    g.replay()
+    torch.cuda.synchronize()
+    eager, eager_lse = sageattn3(q2, k2, v2, return_lse=True)
+    assert torch.equal(prob.out, eager) and torch.equal(prob.lse, eager_lse)
+    assert prob.check_status() == 0
