@@ -196,3 +196,15 @@ def test_cuda_graph_capture_and_replay(cuda_device):
     eager, eager_lse = sageattn3(q2, k2, v2, return_lse=True)
     assert torch.equal(prob.out, eager) and torch.equal(prob.lse, eager_lse)
     assert prob.check_status() == 0
+
+
+@pytest.mark.parametrize("Nq,Nk,causal", [(1, 700, False), (17, 1300, True), (129, 129, True)])
+def test_few_query_rows(cuda_device, Nq, Nk, causal):
+    """Decode-like shapes: a handful of query rows against a long key sequence (one, partly filled, query tile)."""
+    q, k, v = O.make_inputs(1, 4, 2, Nq, Nk, 128, seed=50 + Nq, k_offset_std=1.0)
+    out, lse = sageattn3(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), is_causal=causal, return_lse=True)
+    torch.cuda.synchronize()
+    ref, ref_lse = O.sageattn3_oracle(q, k, v, is_causal=causal, return_lse=True)
+    assert out.shape == (1, 4, Nq, 128)
+    assert O.cosine(out.cpu(), ref) >= COS_MIN and O.rel_l1(out.cpu(), ref) <= RELL1_MAX
+    assert (lse.cpu() - ref_lse).abs().max() <= 1e-3
