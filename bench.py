@@ -347,7 +347,7 @@ def main():
             e2e_ms = t.item()
         nbytes = lambda t_: t_.numel() * t_.element_size()
         e2e = dict(value=world * flops / (e2e_ms * 1e-3) / 1e12, unit="TOPS", ms_per_step=e2e_ms,
-                   h2d_bytes_per_step=nbytes(qh) + nbytes(kh) + nbytes(vh), d2h_bytes_per_step=nbytes(oh))
+                   h2d_bytes_per_step=world * (nbytes(qh) + nbytes(kh) + nbytes(vh)), d2h_bytes_per_step=world * nbytes(oh))     # whole job
 
     if rank != 0:
         if world > 1:
