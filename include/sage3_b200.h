@@ -70,7 +70,8 @@ typedef struct Sage3Desc {
 
 /*
  * Byte offsets of the regions inside the workspace (all multiples of 1024).  Np = N rounded up to 128.
- *   status   int32[64]                        device-written status words (0 = fine)
+ *   status   int32[64]                        device-written status words (0 = fine): [0, 32) pre-pass, [32, 64) attention;
+ *                                             each stage clears its own half, so sage3_check_status after sage3_fwd sees both
  *   kpart    fp32 [B*Hkv][chunks][D]          scratch: partial column sums of K (and of Q when per_block_mean = 0)
  *   km       dtype[B][Hkv][D]                 mean of K over its Nk tokens
  *   qm       dtype[B][Hq][nqm][D]             Q means; nqm = Nq_p/128, or 1 when per_block_mean = 0
@@ -132,14 +133,6 @@ SAGE3_API int sage3_fwd(const Sage3Desc* desc, const void* q, const void* k, con
  * Debugging aid: device-side waits are bounded and report here instead of hanging.
  */
 SAGE3_API int sage3_check_status(const void* ws, int32_t* word, void* stream);
-
-/*
- * Diagnostics variant of sage3_attn_fwd: additionally dumps, for the first query tile of the first
- * (batch, head), the scores of the first processed KV block, its row maxima / partial sums, the final
- * row sums and the unnormalized output accumulators into `debug` (device, 33280 floats).
- * No counterpart in the reference.
- */
-SAGE3_API int sage3_attn_fwd_debug(const Sage3Desc* desc, void* ws, void* out, float* debug, void* stream);
 
 /*
  * Failure-reporting self test: launches one warp that waits, with a limit of about a millisecond, on a barrier

@@ -4,10 +4,17 @@ TEST INFRASTRUCTURE ONLY.  This file is the checker for the CUDA path and the ti
 the benchmark; the product never imports it.  It restates, in torch fp32 on the CPU, the arithmetic of
 the reference's SageAttention3 pipeline, with every rounding point made explicit.
 
-PARITY UNPINNED: the reference ships no tests, golden vectors or fixtures for this path, and its
-kernels only execute on sm_120 hardware, so there is nothing reference-produced to pin this
-restatement against.  What *is* pinned: the E2M1 and E4M3 codecs, against NVIDIA's host-side converters
-in cuda_fp4.h / cuda_fp8.h (oracle/codec_pin.cu -> tests/golden/codec_pin.npz).
+PINNING.  The reference ships no tests, golden vectors or fixtures for this path.  What pins this restatement:
+  * the smoothing + quantization stage (`prepass` below) against the reference itself: its unmodified
+    fp4_quantization_4d.cu (compiled for sm_100a by oracle/build_ref_quant.py) and its unmodified sageattn3/api.py
+    (preprocess_qkv with the Triton block-mean kernel) were run on a B200 on seeded inputs and their outputs stored
+    in tests/golden/ref_prepass.pt (tests/golden/make_ref_prepass_golden.py); tests/test_ref_pin.py holds `prepass`
+    against them: means, smoothed tensors, codes and scale bytes bit for bit, delta_s within one unit in the last place;
+  * the E2M1 and E4M3 codecs against NVIDIA's host-side converters in cuda_fp4.h / cuda_fp8.h
+    (oracle/codec_pin.cu -> tests/golden/codec_pin.npz).
+ATTENTION KERNEL: PARITY UNPINNED.  The reference's attention extension executes on sm_120 hardware only
+(blackwell/api.cu:219-222), so nothing it produced exists to pin `attention_from_prepass` against; it follows the
+cited source lines.
 
 Reference locations (paths inside the reference project):
   sageattention3_blackwell/sageattn3/api.py:75-92      smoothing, padding to 128, delta_s
@@ -111,6 +118,42 @@ def quant_microblocks(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torc
     return codes.flatten(-2), sf_b.squeeze(-1), deq.flatten(-2)
 
 
+def block_mean_16bit_tree(q_blocks: torch.Tensor) -> torch.Tensor:
+    """Mean over the 128 rows of every query block exactly as the reference's Triton kernel forms it
+    (api.py:45-48: `tl.sum(q_group, axis=0) / GROUP_SIZE` on 16-bit data).  Triton does not widen a 16-bit sum, so
+    every addition rounds to the input type and the order matters.  The order below is the one Triton 3.6 generates for
+    this kernel (4 warps, blocked layout, 8 elements per thread along D); it reproduces the reference's means bit for
+    bit on the recorded fixtures (bf16 and fp16, D = 64 and 128):
+      * a thread owns row  rep * R + warp * L + lane_row  of every repetition rep, with L = 32 / (D / 8) rows per
+        warp and R = 4 L rows per repetition; it adds its rows in order of rep;
+      * inside a warp the L partial sums are combined by a butterfly over the lane rows (distance L/2, then L/4, ...);
+      * the four warp sums are combined as (w0 + w2) + (w1 + w3).
+    q_blocks: [..., 128, D] (bf16 / fp16) -> [..., D] in the same type."""
+    dt = q_blocks.dtype
+    D = q_blocks.shape[-1]
+    warps, lane_rows = 4, 32 // (D // 8)
+    reps = BLOCK // (warps * lane_rows)
+
+    def add(a, b):
+        return (a.to(torch.float32) + b.to(torch.float32)).to(dt)
+
+    x = q_blocks.reshape(*q_blocks.shape[:-2], reps, warps, lane_rows, D)
+    acc = x[..., 0, :, :, :]
+    for r in range(1, reps):
+        acc = add(acc, x[..., r, :, :, :])                       # [..., warps, lane_rows, D]
+    vals = [acc[..., i, :] for i in range(lane_rows)]
+    n = lane_rows // 2
+    while n > 0:
+        vals = [add(vals[i], vals[i ^ n]) for i in range(lane_rows)]
+        n //= 2
+    w = [vals[0][..., i, :] for i in range(warps)]
+    n = warps // 2
+    while n > 0:
+        w = [add(w[i], w[i ^ n]) for i in range(warps)]
+        n //= 2
+    return (w[0].to(torch.float32) / BLOCK).to(dt)
+
+
 def pad_rows(x: torch.Tensor, mult: int = BLOCK) -> torch.Tensor:
     """zero-pad dim -2 to a multiple of `mult` (api.py:77-85)."""
     n = x.shape[-2]
@@ -143,8 +186,13 @@ class Prepass:
 
 
 def prepass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, per_block_mean: bool = True,
-            km_override: torch.Tensor | None = None, qm_override: torch.Tensor | None = None) -> Prepass:
+            km_override: torch.Tensor | None = None, qm_override: torch.Tensor | None = None,
+            block_mean: str = "reference") -> Prepass:
     """Smoothing + quantization (api.py:75-116).  q: [B,Hq,Nq,D]; k, v: [B,Hkv,Nk,D]; bf16 or fp16.
+
+    `block_mean`: "reference" forms the per-block Q mean as the reference's Triton kernel does (16-bit additions in
+    its order, see block_mean_16bit_tree); "fp32" sums in fp32 and rounds once (more accurate, but not what the
+    reference computes: about 70 % of the means then differ from the reference's in the last bits).
 
     `km_override` / `qm_override` let a test substitute means computed elsewhere (a different fp32
     summation order can flip the rounding of a mean by one ulp), so that everything downstream of the
@@ -165,11 +213,14 @@ def prepass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, per_block_mean: b
     q_p, k_s, v_p = pad_rows(q), pad_rows(k_s), pad_rows(v)
     Nq_p, Nk_p = q_p.shape[-2], k_s.shape[-2]
 
-    # api.py:86-90 -- Q smoothing.  Pad rows take part in the mean (padding happens first).
+    # api.py:86-90 -- Q smoothing.  Pad rows take part in the mean (padding happens first).  The block mean is a
+    # 16-bit sum in the Triton kernel's order; the subtraction uses the stored (rounded) mean, api.py:50.
     if qm_override is not None:
         qm = qm_override.to(dt)
+    elif per_block_mean and block_mean == "reference":
+        qm = block_mean_16bit_tree(q_p.unflatten(-2, (-1, BLOCK)))                   # [B,Hq,nb,D]
     elif per_block_mean:
-        qm = q_p.to(torch.float32).unflatten(-2, (-1, BLOCK)).mean(dim=-2).to(dt)   # [B,Hq,nb,D]
+        qm = q_p.to(torch.float32).unflatten(-2, (-1, BLOCK)).mean(dim=-2).to(dt)
     else:
         qm = q_p.to(torch.float32).mean(dim=-2, keepdim=True).to(dt)                 # [B,Hq,1,D]
     if per_block_mean:

@@ -15,7 +15,6 @@ SAGE3_FP16, SAGE3_BF16 = 0, 1
 ABI_VERSION = 2          # SAGE3_ABI_VERSION of include/sage3_b200.h this module's structs were written for
 SAGE3_OK = 0
 SAGE3_E_DEVICE_WAIT = -9
-DEBUG_FLOATS = 33280
 
 
 class Sage3Desc(C.Structure):
@@ -69,8 +68,6 @@ def lib() -> C.CDLL:
     l.sage3_prepass.argtypes = [P(Sage3Desc), V, V, V, V, V]
     l.sage3_attn_fwd.restype = C.c_int
     l.sage3_attn_fwd.argtypes = [P(Sage3Desc), V, V, V, V]
-    l.sage3_attn_fwd_debug.restype = C.c_int
-    l.sage3_attn_fwd_debug.argtypes = [P(Sage3Desc), V, V, V, V]
     l.sage3_fwd.restype = C.c_int
     l.sage3_fwd.argtypes = [P(Sage3Desc), V, V, V, V, V, V, V]
     l.sage3_selftest_wait_timeout.restype = C.c_int
@@ -88,7 +85,7 @@ def lib() -> C.CDLL:
 
 
 EXPORTED = ["sage3_version", "sage3_strerror", "sage3_workspace_layout", "sage3_workspace_bytes", "sage3_prepass",
-            "sage3_attn_fwd", "sage3_fwd", "sage3_check_status", "sage3_attn_fwd_debug", "sage3_kmean_noalloc", "sage3_selftest_wait_timeout", "sage3_slab_copy", "sage3_merge_partial"]
+            "sage3_attn_fwd", "sage3_fwd", "sage3_check_status", "sage3_kmean_noalloc", "sage3_selftest_wait_timeout", "sage3_slab_copy", "sage3_merge_partial"]
 
 
 def check(code: int, where: str) -> None:

@@ -132,15 +132,10 @@ class Sage3Problem:
     def _lse_ptr(self):
         return None if self.lse is None else self.lse.data_ptr()
 
-    def attention(self, debug: torch.Tensor | None = None) -> torch.Tensor:
+    def attention(self) -> torch.Tensor:
         with torch.cuda.device(self.device):
-            if debug is None:
-                rc = _cabi.lib().sage3_attn_fwd(C.byref(self.desc), self.ws.buf.data_ptr(), self.out.data_ptr(),
-                                                self._lse_ptr(), self._stream())
-            else:
-                rc = _cabi.lib().sage3_attn_fwd_debug(C.byref(self.desc), self.ws.buf.data_ptr(), self.out.data_ptr(),
-                                                      debug.data_ptr(), self._stream())
-            _cabi.check(rc, "sage3_attn_fwd")
+            _cabi.check(_cabi.lib().sage3_attn_fwd(C.byref(self.desc), self.ws.buf.data_ptr(), self.out.data_ptr(),
+                                                   self._lse_ptr(), self._stream()), "sage3_attn_fwd")
         return self.out
 
     def run(self) -> torch.Tensor:

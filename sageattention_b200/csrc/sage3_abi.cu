@@ -27,6 +27,8 @@ int validate(const Sage3Desc* d) {
     const int64_t nqp = ((int64_t)d->Nq + 127) / 128 * 128, nkp = ((int64_t)d->Nk + 127) / 128 * 128;
     if (nqp > (1 << 24) || nkp > (1 << 24)) return SAGE3_E_TOO_LARGE;
     if ((int64_t)d->B * d->Hq * (nqp / 128) > 0x7fffffffLL) return SAGE3_E_TOO_LARGE;
+    // the pre-pass kernels put the (batch, head) index in gridDim.y
+    if ((int64_t)d->B * d->Hq > 65535) return SAGE3_E_TOO_LARGE;
     return SAGE3_OK;
 }
 
@@ -72,6 +74,10 @@ int check_arch() {
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
+// Status words: [0, 32) belong to the pre-pass, [32, 64) to the attention kernel.  Each stage clears its own half only,
+// so a wait the pre-pass gave up on is still there after the attention launch (whose CTAs read it and exit at once).
+constexpr int kStatusWords = 64, kAttnStatusWord = 32;
+
 int attn_impl(const Sage3Desc* desc, void* ws, void* out, float* lse, float* debug, void* stream) {
     Sage3Workspace w;
     int rc = layout(desc, &w);
@@ -83,7 +89,9 @@ int attn_impl(const Sage3Desc* desc, void* ws, void* out, float* lse, float* deb
     if (rc != SAGE3_OK) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint8_t* base = static_cast<uint8_t*>(ws);
-    if (cudaMemsetAsync(base + w.status, 0, 64 * sizeof(int32_t), st) != cudaSuccess) return SAGE3_E_CUDA;
+    if (cudaMemsetAsync(base + w.status + kAttnStatusWord * sizeof(int32_t), 0, (kStatusWords - kAttnStatusWord) * sizeof(int32_t), st) !=
+        cudaSuccess)
+        return SAGE3_E_CUDA;
     sage3::AttnArgs a;
     a.B = desc->B; a.Hq = desc->Hq; a.Hkv = desc->Hkv; a.Nq = desc->Nq; a.Nk = desc->Nk; a.D = desc->D;
     a.Nq_p = w.nq_pad; a.Nk_p = w.nk_pad; a.nqm = w.nqm;
@@ -99,8 +107,13 @@ int attn_impl(const Sage3Desc* desc, void* ws, void* out, float* lse, float* deb
     a.lse = lse;
     a.qkm = reinterpret_cast<const float*>(base + w.qkm);
     for (int i = 0; i < 3; ++i) a.os[i] = desc->o_stride[i];
-    a.status = reinterpret_cast<int*>(base + w.status);
+    a.status = reinterpret_cast<int*>(base + w.status) + kAttnStatusWord;
+    a.prepass_status = reinterpret_cast<const int*>(base + w.status);
+#ifdef SAGE3_DEV_TRACE
     a.debug = debug;
+#else
+    (void)debug;
+#endif
     int drv = 0;
     return sage3::launch_attn(a, st, &drv) == cudaSuccess ? SAGE3_OK : SAGE3_E_CUDA;
 }
@@ -247,7 +260,7 @@ SAGE3_API int sage3_prepass(const Sage3Desc* desc, const void* q, const void* k,
     a.v_codes = base + w.v_codes; a.v_sf = base + w.v_sf;
     a.qkm = reinterpret_cast<float*>(base + w.qkm);
     a.status = reinterpret_cast<int*>(base + w.status);
-    if (cudaMemsetAsync(base + w.status, 0, 64 * sizeof(int32_t), static_cast<cudaStream_t>(stream)) != cudaSuccess) return SAGE3_E_CUDA;
+    if (cudaMemsetAsync(base + w.status, 0, kStatusWords * sizeof(int32_t), static_cast<cudaStream_t>(stream)) != cudaSuccess) return SAGE3_E_CUDA;
     return sage3::launch_prepass(a, static_cast<cudaStream_t>(stream)) == cudaSuccess ? SAGE3_OK : SAGE3_E_CUDA;
 }
 
@@ -255,9 +268,12 @@ SAGE3_API int sage3_attn_fwd(const Sage3Desc* desc, void* ws, void* out, float* 
     return attn_impl(desc, ws, out, lse, nullptr, stream);
 }
 
+#ifdef SAGE3_DEV_TRACE
+// development builds only (not declared in the public header): attention with the instrumentation dump
 SAGE3_API int sage3_attn_fwd_debug(const Sage3Desc* desc, void* ws, void* out, float* debug, void* stream) {
     return attn_impl(desc, ws, out, nullptr, debug, stream);
 }
+#endif
 
 SAGE3_API int sage3_fwd(const Sage3Desc* desc, const void* q, const void* k, const void* v, void* ws, void* out, float* lse,
               void* stream) {

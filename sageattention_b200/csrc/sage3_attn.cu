@@ -41,15 +41,24 @@
 
 namespace sage3 {
 
-// Optional per-phase cycle accounting of the first CTA (development builds only; off in the product library).
-#ifdef SAGE3_PHASE_TIMING
+// Development instrumentation (compiled only with -DSAGE3_DEV_TRACE; the product library has none of it):
+// per-phase cycle sums of every softmax warp of the first CTA, a time line of a few KV blocks, and a dump of
+// the first block's scores, statistics and accumulators of the first query tile.
+#ifdef SAGE3_DEV_TRACE
 #define PT_DECL long long pt_t = clock64(); long long pt_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #define PT(i) { const long long pt_now = clock64(); pt_acc[i] += pt_now - pt_t; pt_t = pt_now; }
 #define PT_DUMP(slot) if (p.debug != nullptr && blockIdx.x == 0 && lane == 0) { for (int i_ = 0; i_ < 8; ++i_) p.debug[40000 + (slot) * 8 + i_] = (float)pt_acc[i_]; }
+// time line: event `ev` (0..15) of actor `who` (0..23) at loop index `it`, for kTrIters iterations from kTrFirst on
+constexpr int kTrFirst = 40, kTrIters = 4;
+#define TR(who, it, ev) if (p.debug != nullptr && blockIdx.x == 0 && lane == 0 && (it) >= kTrFirst && (it) < kTrFirst + kTrIters) \
+    { p.debug[42000 + ((who) * kTrIters + ((it) - kTrFirst)) * 16 + (ev)] = __uint_as_float((uint32_t)clock64()); }
+#define DEV_DUMP(...) __VA_ARGS__
 #else
 #define PT_DECL
 #define PT(i)
 #define PT_DUMP(slot)
+#define TR(who, it, ev)
+#define DEV_DUMP(...)
 #endif
 
 constexpr float kLog2Of6 = 2.584962500721156f;
@@ -67,7 +76,10 @@ struct AttnParams {
     const float* qkm;                   // fp32 [B*Hq][nqt*128]: q . km per query row
     float sm_scale;
     int* status;
-    float* debug;                       // optional dump of CTA 0, tile 0 (nullptr in normal use)
+    const int* prepass_status;
+#ifdef SAGE3_DEV_TRACE
+    float* debug;                       // development dump of CTA 0 (nullptr in normal use)
+#endif
 };
 
 template <int D>
@@ -164,7 +176,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int b = bhq / p.Hq, hq = bhq % p.Hq;
     const int bhkv = b * p.Hkv + hq / (p.Hq / p.Hkv);
     const int shift = p.Nk - p.Nq;
-    const bool dead_launch = (*reinterpret_cast<volatile int*>(p.status) != 0);   // an earlier CTA gave up
+    // an earlier CTA of this launch gave up, or the pre-pass did (the workspace is then incomplete)
+    const bool dead_launch = (*reinterpret_cast<volatile int*>(p.status) != 0) || (*reinterpret_cast<const volatile int*>(p.prepass_status) != 0);
     // KV blocks of tile t: [0, nbt[t]); the CTA walks block n = nbmax - 1 ... 0 and tile t joins at step skip[t]
     int nbt[2];
 #pragma unroll
@@ -280,6 +293,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             for (int jj = 0; ok && jj < nbmax; ++jj) {
                 const int st = jj % S;
                 if (!mbar_wait(bar(bKF + st), (jj / S) & 1, abort_flag, p.status, kWaitKFull)) { ok = false; break; }
+                TR(16, jj, 8)
                 tc_fence_after();
                 const uint64_t k_desc = make_sdesc(sbase + C::oK + st * 8192, 16, C::kSboQK, C::kSwzQK);
 #pragma unroll
@@ -288,6 +302,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 for (int t = 0; t < 2; ++t) {
                     if (jj < skip[t]) continue;
                     if (uses > 0 && !mbar_wait(bar(bSE), (uses - 1) & 1, abort_flag, p.status, kWaitSEmpty)) { ok = false; break; }
+                    TR(16, jj, 4 * t)
                     tc_fence_after();
                     const uint64_t q_desc = make_sdesc(sbase + C::oQ + t * 8192, 16, C::kSboQK, C::kSwzQK);
                     // S <- 1 (x) delta_s: A = [128 x 16] with ones in column 0 (K-major), B = the delta_s row read as an
@@ -299,6 +314,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                         tc_mma_nvfp4(tmem + C::cS, q_desc + 2 * ks, k_desc + 2 * ks, idesc_qk,
                                      tmem + C::cSfQ + 8 * t + 4 * ks, tmem + C::cSfK + 4 * ks, true);
                     tc_commit(bar(bSF + t));
+                    TR(16, jj, 4 * t + 1)
                     ++uses;
                 }
                 if (ok) tc_commit(bar(bKE + st));
@@ -313,12 +329,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             for (int jj = 0; ok && jj < nbmax; ++jj) {
                 const int st = jj % S;
                 if (!mbar_wait(bar(bVF + st), (jj / S) & 1, abort_flag, p.status, kWaitVFull)) break;
+                TR(17, jj, 8)
                 const uint64_t v_desc = make_sdesc(sbase + C::oV + st * 8192, 16, 512, kSwz64);
                 bool first = true;
                 for (int t = 0; t < 2; ++t) {
                     if (jj < skip[t]) continue;
                     const int j = jj - skip[t], pb = t * 2 + (j & 1);
                     if (!mbar_wait(bar(bPF + pb), (j >> 1) & 1, abort_flag, p.status, kWaitPFull)) { ok = false; break; }
+                    TR(17, jj, 4 * t)
                     tc_fence_after();
                     if (first) {
 #pragma unroll
@@ -335,6 +353,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                         tc_mma_nvfp4(tmem + C::cO + t * 128, p_desc + 2 * ks, v_desc + 2 * ks, idesc_pv, tmem + C::cSfP + 4 * ks,
                                      tmem + C::cSfV + 4 * ks, (j > 0) || (ks > 0));
                     tc_commit(bar(bPV + pb));
+                    TR(17, jj, 4 * t + 1)
                 }
                 if (ok) tc_commit(bar(bVE + st));
             }
@@ -361,7 +380,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const uint32_t o_addr = tmem + lane_addr + C::cO + t * 128 + (D / 2) * h;
         const int sw = (r >> 1) & 3;
         const uint64_t sl2x2 = pack2f(sl2, sl2);
-        const bool dbg = (p.debug != nullptr && blockIdx.x == 0 && t == 0);
+        DEV_DUMP(const bool dbg = (p.debug != nullptr && blockIdx.x == 0 && t == 0);)
         float* xch_mine = reinterpret_cast<float*>(sgen + C::oXch) + (t * 2 + h) * 128 + r;
         const float* xch_other = reinterpret_cast<float*>(sgen + C::oXch) + (t * 2 + (h ^ 1)) * 128 + r;
         const uint32_t bar_x = bar(bXC + t * 4 + quarter);
@@ -371,7 +390,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         PT_DECL
         for (int j = 0; j < nb; ++j) {
             const int n = nb - 1 - j, pb = t * 2 + (j & 1);
+            TR(warp - 4, j, 0)
             if (!warp_wait(bar(bSF + t), j & 1, abort_flag, p.status, kWaitSFull)) { alive = false; break; }
+            TR(warp - 4, j, 1)
             PT(0)
             tc_fence_after();
             float s[64];
@@ -381,6 +402,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(bSE));     // S is in registers: the other tile's Q K^T may overwrite it
+            TR(warp - 4, j, 2)
             PT(1)
             const bool need_mask = ((n + 1) * kBlock > p.Nk) || (CAUSAL && (n * kBlock + kBlock - 1 > mt * kBlock + shift));
             if (need_mask) {
@@ -391,10 +413,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 for (int i = 0; i < 64; ++i)
                     if (key0 + i > lim) s[i] = -INFINITY;
             }
-            if (dbg && j == 0) {
-#pragma unroll
+            DEV_DUMP(if (dbg && j == 0) {
                 for (int i = 0; i < 64; ++i) p.debug[r * 128 + 64 * h + i] = s[i];
-            }
+            })
             // microblock maxima of this half; the half maximum goes to the partner thread
             float bm[4];
             microblock_max2(s, bm[0], bm[1]);
@@ -403,6 +424,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             xch_mine[(j & 1) * 512] = m_half;
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_x);
+            TR(warp - 4, j, 3)
             PT(2)
             // exp2 pass: E = P~ / sf = 6 * 2^((S - bm) s) needs the microblock maximum only, not the row maximum
             uint32_t codes[8];
@@ -432,18 +454,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 codes[2 * g] = cvt_e2m1x8(e[0], e[1], e[2], e[3], e[4], e[5], e[6], e[7]);
                 codes[2 * g + 1] = cvt_e2m1x8(e[8], e[9], e[10], e[11], e[12], e[13], e[14], e[15]);
             }
+            TR(warp - 4, j, 4)
             PT(3)
             // running maximum (with the partner's half, published before its own exp2 pass), rescale factor,
             // E4M3 scale sf = max(P~) / 6 = 2^(bm s - max_scaled - log2 6) of every microblock, weighted sum
             if (!warp_wait(bar_x, xphase, abort_flag, p.status, kWaitPair)) { alive = false; break; }
             xphase ^= 1;
+            TR(warp - 4, j, 5)
             const float m_new = fmax3(m_run, m_half, xch_other[(j & 1) * 512]);
             const bool empty = (m_new == -INFINITY);
             const float m_cur = empty ? 0.f : m_new;
             const float alpha = ex2_approx((m_run - m_cur) * sl2);        // m_run = -inf  ->  0
             const float max_scaled = empty ? 0.f : fmaf(m_new, sl2, kPScaleLog2);
             m_run = m_new;
-            if (dbg && j == 0 && h == 0) p.debug[16384 + r] = m_new;
+            DEV_DUMP(if (dbg && j == 0 && h == 0) p.debug[16384 + r] = m_new;)
             uint32_t sfb = 0;
             float rowsum = 0.f;
 #pragma unroll
@@ -453,9 +477,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 sfb |= (cvt_e4m3x2(sfv, 0.f) & 0xffu) << (8 * g);
             }
             l_run = fmaf(l_run, alpha, rowsum);      // partial row sum of this thread's keys
-            if (dbg && j == 0) p.debug[16384 + 128 + 128 * h + r] = rowsum;
+            DEV_DUMP(if (dbg && j == 0) p.debug[16384 + 128 + 128 * h + r] = rowsum;)
             // P buffer j & 1 was last read by the PV MMA of block j - 2
             if (j >= 2 && !warp_wait(bar(bPV + pb), ((j >> 1) - 1) & 1, abort_flag, p.status, kWaitPEmpty)) { alive = false; break; }
+            TR(warp - 4, j, 6)
             PT(4)
             // P codes: this half's two 16-byte chunks of the 64-byte-swizzled K-major row; scales: its 64-key atom
             uint8_t* prow = sgen + C::oP + pb * C::kPBytes + r * 64;
@@ -466,6 +491,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     make_uint4(codes[4 * c], codes[4 * c + 1], codes[4 * c + 2], codes[4 * c + 3]);
             sfp_row[128 * h] = sfb;
             fence_proxy_async_smem();
+            TR(warp - 4, j, 7)
             PT(5)
             // This thread's half of the O row times alpha before the block's P V is added (only when a row of the
             // warp moved its maximum); the P V MMA of block j - 1 must have landed first
@@ -484,10 +510,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     tmem_st32(o_addr + cc * 32, o0);
                 }
                 tc_wait_st();
+                TR(warp - 4, j, 8)
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(bPF + pb));
+            TR(warp - 4, j, 9)
             PT(6)
         }
         PT_DUMP(warp)
@@ -526,11 +554,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
                         for (int i = 0; i < 32; ++i) o[i] = 0.f;
                     }
-                    if (dbg) {
-#pragma unroll
+                    DEV_DUMP(if (dbg) {
                         for (int i = 0; i < 32; ++i) p.debug[16384 + 512 + r * D + (D / 2) * h + cc * 32 + i] = o[i];
                         if (cc == 0 && h == 0) p.debug[16384 + 384 + r] = l_tot;
-                    }
+                    })
                     if (grow < p.Nq) {
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
@@ -630,7 +657,10 @@ cudaError_t launch_attn(const AttnArgs& a, cudaStream_t st, int* driver_rc) {
     p.lse = a.lse; p.qkm = a.qkm; p.sm_scale = a.sm_scale;
     p.os0 = a.os[0]; p.os1 = a.os[1]; p.os2 = a.os[2];
     p.status = a.status;
+    p.prepass_status = a.prepass_status;
+#ifdef SAGE3_DEV_TRACE
     p.debug = a.debug;
+#endif
     if (a.is_bf16) {
         if (a.D == 128) return a.is_causal ? launch_t<128, true, __nv_bfloat16>(a, tq, tk, tv, p, st)
                                            : launch_t<128, false, __nv_bfloat16>(a, tq, tk, tv, p, st);

@@ -16,7 +16,7 @@ constexpr int kMicro = 16;    // NVFP4 microblock
 enum : int {
     kWaitQFull = 101, kWaitKFull = 102, kWaitVFull = 103, kWaitKEmpty = 104, kWaitVEmpty = 105,
     kWaitSFull = 106, kWaitSEmpty = 107, kWaitPFull = 108, kWaitOReady = 109, kWaitPair = 110,
-    kWaitDelta = 111, kWaitOScaled = 112, kWaitPEmpty = 113, kWaitAlpha = 114, kWaitStats = 115, kWaitDeltaMma = 116, kWaitSelfTest = 199
+    kWaitPEmpty = 113, kWaitDeltaMma = 116, kWaitSelfTest = 199
 };
 
 // ------------------------------------------------------------------------------------------------

@@ -32,8 +32,11 @@ struct AttnArgs {
     int64_t os[3];
     float* lse;                     // optional fp32 [B][Hq][Nq]; nullptr if not wanted
     const float* qkm;               // fp32 [B][Hq][Nq_p] from the pre-pass
-    int* status;
-    float* debug;                   // optional diagnostics dump of the first CTA; nullptr in normal use
+    int* status;                    // the attention kernel's status word
+    const int* prepass_status;      // the pre-pass's status word (non-zero: the workspace is incomplete, do nothing)
+#ifdef SAGE3_DEV_TRACE
+    float* debug;                   // development dump of the first CTA; nullptr in normal use
+#endif
 };
 
 cudaError_t launch_prepass(const PrepassArgs& a, cudaStream_t st);

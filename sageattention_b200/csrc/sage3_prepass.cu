@@ -4,7 +4,7 @@
 //
 // Math follows (paths inside the reference project, sageattention3_blackwell/sageattn3/...):
 //   api.py:84            k' = k - mean_N(k)                 (mean: fp32 sum, rounded to the input type)
-//   api.py:55-72, 86-90  q' = q - mean of each 128-row block (or of all padded rows)
+//   api.py:26-72, 86-90  q' = q - mean of each 128-row block (16-bit additions in the Triton kernel's order) or of all padded rows
 //   api.py:91            delta_s = qm . k'^T, rounded to the input type (tcgen05 16-bit MMA, accumulator in TMEM)
 //   quantization/fp4_quantization_4d.cu:185-225   SF = e4m3(amax / 6), code = e2m1(x * (1 / SF))
 //   quantization/fp4_quantization_4d.cu:300-349   V: microblocks are 16 consecutive tokens of one channel
@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(256, 3) quant_rows_kernel(
     extern __shared__ __align__(16) uint8_t smem_raw[];
     float* s_mean = reinterpret_cast<float*>(smem_raw);                        // [D]
     uint8_t* s_sf = smem_raw + D * 4;                                          // [(D/64) * 512]
-    float* s_red = reinterpret_cast<float*>(s_sf + (D / 64) * 512);            // [8 warps][D] (block mean)
+    uint8_t* s_more = s_sf + (D / 64) * 512;                                   // block mean only: staged tile, chain sums
 
     uint4 raw[ITEMS][2];
 #pragma unroll
@@ -181,34 +181,66 @@ __global__ void __launch_bounds__(256, 3) quant_rows_kernel(
     }
 
     if (MODE == kModeQBlockMean) {
-        // column sums over the tile's 128 rows (rows beyond N are zero and count, as padding precedes the mean)
-        float acc[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+        // Block mean exactly as the reference's Triton kernel forms it (api.py:45-48): a sum of 16-bit values whose every
+        // addition rounds to the input type, in the order of that kernel's 4-warp blocked layout:
+        //   chain (w, l): rows rep * R + w * L + l, rep = 0 .. 128 / R - 1, added in order of rep
+        //                 (L = 32 / (D / 8) rows of a warp, R = 4 L rows per repetition),
+        //   then a butterfly over l inside each warp (distance L/2, L/4, ...), then (w0 + w2) + (w1 + w3).
+        // Rows beyond N are zero and take part (padding precedes the mean).  The tile is staged in shared memory so
+        // that one thread can walk one chain for four columns.
+        constexpr int L = 32 / (D / 8), R = 4 * L, REPS = kBlock / R;
+        static_assert(R * (D / 4) == 256, "one thread per (chain, group of four columns)");
+        T* s_tile = reinterpret_cast<T*>(s_more);                              // [128][D]
+        T* s_part = s_tile + kBlock * D;                                       // [R][D]
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
-            float f[16];
-            unpack16<T>(raw[i][0], raw[i][1], f);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) acc[j] += f[j];
+            uint4* dst = reinterpret_cast<uint4*>(s_tile + (rl + RPP * i) * D + c * 16);
+            dst[0] = raw[i][0];
+            dst[1] = raw[i][1];
         }
-        // lanes sharing c inside a warp: lane = c + CH * k
+        __syncthreads();
+        {
+            const int chain = t / (D / 4), c4 = (t % (D / 4)) * 4;
+            auto add_t = [](float a, float b) { return Num<T>::to_f(Num<T>::from_f(a + b)); };
+            float acc[4];
+            {
+                const uint2 w0 = *reinterpret_cast<const uint2*>(s_tile + chain * D + c4);
+                const float2 lo = Num<T>::to_f2(w0.x), hi = Num<T>::to_f2(w0.y);
+                acc[0] = lo.x; acc[1] = lo.y; acc[2] = hi.x; acc[3] = hi.y;
+            }
 #pragma unroll
-        for (int off = CH; off < 32; off <<= 1) {
+            for (int rep = 1; rep < REPS; ++rep) {
+                const uint2 w1 = *reinterpret_cast<const uint2*>(s_tile + (rep * R + chain) * D + c4);
+                const float2 lo = Num<T>::to_f2(w1.x), hi = Num<T>::to_f2(w1.y);
+                acc[0] = add_t(acc[0], lo.x); acc[1] = add_t(acc[1], lo.y);
+                acc[2] = add_t(acc[2], hi.x); acc[3] = add_t(acc[3], hi.y);
+            }
 #pragma unroll
-            for (int j = 0; j < 16; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
-        }
-        const int warp = t >> 5, lane = t & 31;
-        if (lane < CH) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) s_red[warp * D + lane * 16 + j] = acc[j];
+            for (int j = 0; j < 4; ++j) s_part[chain * D + c4 + j] = Num<T>::from_f(acc[j]);
         }
         __syncthreads();
         if (t < D) {
-            float s = 0.f;
+            float v[4][L];
 #pragma unroll
-            for (int w = 0; w < 8; ++w) s += s_red[w * D + t];
-            const T m = Num<T>::from_f(s * (1.0f / kBlock));
+            for (int w = 0; w < 4; ++w)
+#pragma unroll
+                for (int l = 0; l < L; ++l) v[w][l] = Num<T>::to_f(s_part[(w * L + l) * D + t]);
+            auto add_t = [](float a, float b) { return Num<T>::to_f(Num<T>::from_f(a + b)); };
+            float wsum[4];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+#pragma unroll
+                for (int n = L / 2; n > 0; n >>= 1) {
+                    float nv[L];
+#pragma unroll
+                    for (int l = 0; l < L; ++l) nv[l] = add_t(v[w][l], v[w][l ^ n]);
+#pragma unroll
+                    for (int l = 0; l < L; ++l) v[w][l] = nv[l];
+                }
+                wsum[w] = v[w][0];
+            }
+            const float tot = add_t(add_t(wsum[0], wsum[2]), add_t(wsum[1], wsum[3]));
+            const T m = Num<T>::from_f(tot * (1.0f / kBlock));
             s_mean[t] = Num<T>::to_f(m);
             qm_out[((int64_t)bh * (Np / kBlock) + tile) * D + t] = m;
         }
@@ -493,9 +525,11 @@ static cudaError_t launch_prepass_t(const PrepassArgs& a, cudaStream_t st) {
                                                                          a.kpart, a.kchunks_k);
     colmean_finalize_kernel<T, D><<<BHkv, D, 0, st>>>(a.kpart, a.kchunks_k, 1.0f / (float)a.Nk, km);
 
-    const size_t smem_q = D * 4 + (D / 64) * 512 + 8 * D * 4;
+    const size_t smem_q = D * 4 + (D / 64) * 512;
     if (a.per_block_mean) {
-        quant_rows_kernel<T, D, kModeQBlockMean><<<dim3(a.Nq_p / kBlock, BHq), 256, smem_q, st>>>(
+        // + the staged tile [128][D] and the chain sums [4 * 32 / (D / 8)][D] of the block mean
+        const size_t smem_qb = smem_q + (kBlock + 4 * (32 / (D / 8))) * D * sizeof(T);
+        quant_rows_kernel<T, D, kModeQBlockMean><<<dim3(a.Nq_p / kBlock, BHq), 256, smem_qb, st>>>(
             q, a.qs[0], a.qs[1], a.qs[2], a.Hq, a.Nq, a.Nq_p, nullptr, qm, a.q_codes, a.q_sf, km, a.Hq / a.Hkv, a.qkm);
     } else {
         // one mean per head over the padded rows (api.py:88-90); kpart is free again: the K finalize has

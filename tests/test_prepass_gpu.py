@@ -1,4 +1,5 @@
-"""GPU parity of the pre-pass, through the C ABI: means within one ulp of the oracle's, and everything
+"""GPU parity of the pre-pass, through the C ABI: the Q block means bit for bit (a 16-bit sum in the reference's order),
+the fp32-accumulated means (K, and Q when per_block_mean is off) within one ulp of the oracle's, and everything
 downstream of the means (smoothed values -> codes, scale bytes, delta_s) bit for bit / within one ulp."""
 import pytest
 import torch
@@ -40,7 +41,11 @@ def test_prepass_matches_oracle(cuda_device, B, Hq, Hkv, Nq, Nk, D, dt, pbm, lay
 
     ref0 = O.prepass(q, k, v, per_block_mean=pbm)
     assert _ulp_close(ws["km"], ref0.km), "K mean"
-    assert _ulp_close(ws["qm"], ref0.qm), "Q mean"
+    if pbm:
+        # the block mean is a 16-bit sum in the reference's (Triton) order: identical, not just close
+        assert torch.equal(ws["qm"], ref0.qm), "Q block mean"
+    else:
+        assert _ulp_close(ws["qm"], ref0.qm), "Q mean"
     # everything after the means, with the device's means substituted: must be identical
     ref = O.prepass(q, k, v, per_block_mean=pbm, km_override=ws["km"], qm_override=ws["qm"])
     assert torch.equal(ws["q_sf"], ref.q_sf), "Q scale bytes"
