@@ -9,7 +9,10 @@ reference's headline "attention TOPS at hd128, N=32k" is quoted on.  TOPS = 4*B*
 
 With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank runs the whole workload on its
 own (batch, head) shard with no data-path collective (weak scaling); the reported value is the units all
-ranks processed divided by the slowest rank's device time.
+ranks processed divided by the slowest rank's device time.  The same line carries, under "ulysses", the
+strong-scaling arm of the two long-sequence video workloads (tokens sharded over the ranks, all-to-all before and
+after attention; at N = 1 the plain call on the same workload), and under "parity" a check of the timed output: one
+whole query tile of one head against the CPU oracle.
 
 `--impl reference` times the reference's math on the host cores instead: the torch-fp32 CPU restatement of
 the reference pipeline (the reference's own kernels only execute on sm_120 hardware), on a bounded sample
@@ -119,19 +122,66 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------------------------------
-def cpu_reference_sample(w, seconds_target: float = 2.0):
-    """One bounded sample of the workload on the host cores with the CPU oracle: one (batch, head) at a
-    reduced sequence length.  Returns (flops, seconds, description)."""
+def cpu_reference_sample(w, n: int | None = None, heads: int | None = None):
+    """One bounded sample of the workload on the host cores with the CPU oracle: `heads` query heads (default: the
+    query heads of one kv head) of one batch entry at sequence length `n` (default min(N, 4096)), same dtype, head
+    dim, mask and input distributions.  Returns (flops, seconds, description)."""
     import torch
     from oracle import sage3_oracle as O
-    n = min(w["Nq"], 4096)
+    n = min(w["Nq"], 4096) if n is None else n
     group = w["Hq"] // w["Hkv"]
-    q, k, v = O.make_inputs(1, group, 1, n, n, w["D"], seed=4242, **w["inp"])
+    hq = group if heads is None else heads
+    hkv = max(1, hq // group)
+    q, k, v = O.make_inputs(1, hq, hkv, n, n, w["D"], seed=4242, **w["inp"])
     t0 = time.perf_counter()
     O.sageattn3_oracle(q, k, v, is_causal=w["causal"])
     dt = time.perf_counter() - t0
-    f = 4.0 * group * n * n * w["D"] / (2 if w["causal"] else 1)
-    return f, dt, f"{group} query head(s) of one (batch, kv-head) at Nq=Nk={n}, D={w['D']}, same distributions"
+    f = 4.0 * hq * n * n * w["D"] / (2 if w["causal"] else 1)
+    return f, dt, f"{hq} query head(s) of one batch entry at Nq=Nk={n}, D={w['D']}, same distributions"
+
+
+def cpu_baseline_report(w, cores: int, budget_s: float = 14.0):
+    """The CPU oracle timed on the host cores: the small configuration at its full size, then one head of the
+    benchmark workload at N = 4096 and N = 8192; the full-length figure is an extrapolation (time grows with N^2
+    at fixed width) and is labelled as one."""
+    import torch
+    torch.set_num_threads(cores)
+    c1 = WORKLOADS["c1_small"]
+    out, t_start = {}, time.perf_counter()
+    f, dt, _ = cpu_reference_sample(c1, n=c1["Nq"], heads=c1["Hq"])          # warm-up (thread pool, allocator)
+    f, dt, d1 = cpu_reference_sample(c1, n=c1["Nq"], heads=c1["Hq"])
+    out["c1_small_full_size"] = dict(tops=f / dt / 1e12, seconds=dt, sample=d1)
+    best = None
+    for n in (4096, 8192):
+        if n > w["Nq"] or time.perf_counter() - t_start > budget_s:
+            break
+        f, dt, dn = cpu_reference_sample(w, n=n)
+        out[f"N{n}"] = dict(tops=f / dt / 1e12, seconds=dt, sample=dn)
+        best = (f / dt / 1e12, n, dt, dn)
+    if best is None:
+        f, dt, dn = cpu_reference_sample(w)
+        best = (f / dt / 1e12, min(w["Nq"], 4096), dt, dn)
+    tops, n, dt, dn = best
+    group = w["Hq"] // w["Hkv"]
+    full_s = dt * (w["Nq"] / n) ** 2 * (w["B"] * w["Hq"] / group)
+    return dict(value=tops, unit="TOPS", cores=cores, kind="port", sample=dn, measured=out,
+                extrapolated_seconds_for_the_whole_workload=full_s,
+                extrapolation="EXTRAPOLATED, not measured: time of the largest measured sample x (N / n)^2 x (batch x heads)")
+
+
+def parity_of_timed_output(w, qh, kh, vh, oh, tile: int | None = None):
+    """One whole 128-row query tile of the output the timed steps produced, against the CPU oracle run on the same
+    inputs.  qh / oh: [1, group, N, D] host tensors (the query heads of kv head 0 of batch 0), kh / vh: [1, 1, N, D].
+    The oracle quantizes the whole head, then evaluates the sampled rows against all keys."""
+    from oracle import sage3_oracle as O
+    nt = (w["Nq"] + 127) // 128
+    tile = nt // 3 if tile is None else tile
+    rows = slice(tile * 128, min(w["Nq"], (tile + 1) * 128))
+    pp = O.prepass(qh, kh, vh)
+    ref = O.attention_from_prepass(pp, is_causal=w["causal"], q_rows=slice(tile * 128, (tile + 1) * 128))
+    got = oh[:, :, rows]
+    return dict(cos=O.cosine(got, ref), rel_l1=O.rel_l1(got, ref), rows=f"batch 0, kv head 0, query rows {rows.start}..{rows.stop - 1}",
+                gate="cos >= 0.999 and rel_l1 <= 0.01 against the CPU oracle")
 
 
 def run_reference(args, w):
@@ -158,47 +208,111 @@ def run_reference(args, w):
     print(json.dumps(line))
 
 
-def run_ulysses(args, w, q, k, v, flops, rank, world, local, dev):
-    """Strong-scaling arm: one step = all-to-all, pre-pass, attention, all-to-all on every rank."""
+def make_inputs_on_device(w, dev, seed, Nq=None, Nk=None):
+    """Seeded synthetic input of a workload, generated on the device (the full tensors are several GB)."""
+    import torch
+    g = torch.Generator(device=dev).manual_seed(seed)
+    B, Hq, Hkv, D = (w[k_] for k_ in ("B", "Hq", "Hkv", "D"))
+    Nq, Nk = (w["Nq"] if Nq is None else Nq), (w["Nk"] if Nk is None else Nk)
+    shp_q = (B, Hq, Nq, D) if w["layout"] == "HND" else (B, Nq, Hq, D)
+    shp_k = (B, Hkv, Nk, D) if w["layout"] == "HND" else (B, Nk, Hkv, D)
+    q = torch.empty(shp_q, dtype=torch.bfloat16, device=dev).normal_(generator=g)
+    k = torch.empty(shp_k, dtype=torch.bfloat16, device=dev).normal_(generator=g)
+    v = torch.empty(shp_k, dtype=torch.bfloat16, device=dev).normal_(generator=g)
+    off_std = w["inp"].get("k_offset_std", 0.0)
+    if off_std:
+        off_shape = (B, Hkv, 1, D) if w["layout"] == "HND" else (B, 1, Hkv, D)
+        k += (off_std * torch.randn(off_shape, device=dev, generator=g)).to(torch.bfloat16)
+    if w["inp"].get("k_outlier_channels"):
+        idx = torch.randperm(D, device=dev, generator=g)[: w["inp"]["k_outlier_channels"]]
+        k[..., idx] *= 2
+    # (RoPE of the Llama-shaped workload changes values, not shapes or timing; the parity tests cover it.)
+    return q, k, v
+
+
+def time_sequence_parallel(name, steps, warmup, rank, world, dev, ring=False, overlap_groups=1):
+    """Strong-scaling arm on workload `name`: every rank holds the token shard [rank N/P, (rank + 1) N/P) of all heads;
+    one step = all-to-all, pre-pass, attention, all-to-all (at one GPU: the plain call).  Device time, max over ranks."""
     import torch
     import torch.distributed as dist
+    from sageattention_b200 import sageattn3
     from sageattention_b200.ulysses import ring_attention, ulysses_attention
-    if args.ring:        # same token shards, K / V shards travel around the ring instead of the two all-to-alls
-        ulysses_attention = lambda q_, k_, v_, tensor_layout, overlap_groups: ring_attention(q_, k_, v_, tensor_layout=tensor_layout)
+    w = WORKLOADS[name]
+    if w["Nq"] % world or w["Hq"] % world or w["Hkv"] % world or w["causal"]:
+        return dict(skipped=f"token / head counts of {name} are not divisible by {world} GPUs")
+    q, k, v = make_inputs_on_device(w, dev, 7000 + rank, w["Nq"] // world, w["Nk"] // world)
     stream = torch.cuda.current_stream()
-    hkv_l = w["Hkv"] // world
-    groups = max(1, min(args.overlap_groups if args.overlap_groups else 1, hkv_l))      # ulysses_attention's own rule
-    for _ in range(max(args.warmup, 3)):
-        ulysses_attention(q, k, v, tensor_layout=w["layout"], overlap_groups=groups)
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    dist.barrier()
+    prof = []
+
+    def step(profile=None):
+        if world == 1:
+            return sageattn3(q, k, v, tensor_layout=w["layout"])
+        if ring:
+            return ring_attention(q, k, v, tensor_layout=w["layout"])
+        return ulysses_attention(q, k, v, tensor_layout=w["layout"], overlap_groups=overlap_groups, profile=profile)
+
+    for _ in range(max(warmup, 3)):
+        step()
+    if world > 1:
+        dist.barrier()
     torch.cuda.synchronize()
     a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record(stream)
-    for _ in range(args.steps):
-        ulysses_attention(q, k, v, tensor_layout=w["layout"], overlap_groups=groups)
+    for _ in range(steps):
+        step()
     b_.record(stream)
     torch.cuda.synchronize()
-    dist.barrier()
-    clocks = sampler.stop() if rank == 0 else None
-    t = torch.tensor([a.elapsed_time(b_) / args.steps], device=dev, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = t.item()
+    ms = a.elapsed_time(b_) / steps
+    split = None
+    if world > 1 and not ring:
+        step(prof)                                   # one more step with phase marks, outside the timed region
+        torch.cuda.synchronize()
+        ev = dict(prof)
+        if all(n_ in ev for n_ in ("start", "exchanged_in", "attended", "exchanged_out")):
+            split = [ev["start"].elapsed_time(ev["exchanged_in"]), ev["exchanged_in"].elapsed_time(ev["attended"]),
+                     ev["attended"].elapsed_time(ev["exchanged_out"])]
+        t = torch.tensor([ms] + (split or [0.0, 0.0, 0.0]), device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, split = t[0].item(), (t[1:].tolist() if split else None)
+    elif world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    del q, k, v
+    torch.cuda.empty_cache()
+    res = dict(tops=flops_of(w) / (ms * 1e-3) / 1e12, ms_per_step=ms, steps=steps, scaling="strong",
+               tokens_per_rank=w["Nq"] // world, heads_per_rank=w["Hq"] // world,
+               sharding=("one GPU: plain call" if world == 1 else
+                         "ring attention (NCCL send/recv of K/V shards, LSE merge)" if ring else
+                         "ulysses sequence parallel: NCCL all-to-all before and after attention"))
+    if split:
+        res.update(exchange_in_ms=split[0], attn_ms=split[1], exchange_out_ms=split[2], a2a_ms=split[0] + split[2])
+        res["all_to_all_bytes_per_rank_per_step"] = 4 * (world - 1) / world * (w["B"] * w["Hq"] * (w["Nq"] // world) * w["D"]) * 2
+    return res
+
+
+def run_ulysses(args, w, rank, world, local, dev):
+    """`--ulysses`: the strong-scaling arm alone, as its own JSON line."""
+    import torch.distributed as dist
+    sampler = ClockSampler(local)
     if rank == 0:
-        per_rank_bytes = 4 * (world - 1) / world * q.numel() * 2      # q, k, v out and o back, 16-bit
+        sampler.start()
+    res = time_sequence_parallel(args.workload, args.steps, args.warmup, rank, world, dev, ring=args.ring,
+                                 overlap_groups=max(1, args.overlap_groups))
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        if "skipped" in res:
+            raise SystemExit(res["skipped"])
+        groups = max(1, args.overlap_groups)
         print(json.dumps(dict(
-            metric="attention TOPS (4*B*H*Nq*Nk*D/t) of the smooth+NVFP4-quantize+attend path", value=flops / (ms * 1e-3) / 1e12, unit="TOPS",
-            n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=ms, higher_is_better=True, scaling="strong",
-            vs_baseline=None, dtype="fp4 (e2m1 x ue4m3), fp32 accumulate", data="synthetic",
-            config=dict(workload=args.workload, sharding=("ring attention: K/V shards sent around the ring (NCCL send/recv), partial results merged by LSE"
-                                                          if args.ring else "ulysses sequence parallel: NCCL all-to-all before and after attention"),
-                        tokens_per_rank=q.shape[2] if w["layout"] == "HND" else q.shape[1], heads_per_rank=w["Hq"] // world,
-                        all_to_all_bytes_per_rank_per_step=per_rank_bytes, head_slices_in_flight=groups,
-                        l2="inputs larger than L2"),
+            metric="attention TOPS (4*B*H*Nq*Nk*D/t) of the smooth+NVFP4-quantize+attend path", value=res["tops"], unit="TOPS",
+            n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=res["ms_per_step"], higher_is_better=True,
+            scaling="strong", vs_baseline=None, dtype="fp4 (e2m1 x ue4m3), fp32 accumulate", data="synthetic",
+            config=dict(workload=args.workload, l2="inputs larger than L2", head_slices_in_flight=groups,
+                        **{k_: v_ for k_, v_ in res.items() if k_ not in ("tops", "ms_per_step", "steps", "scaling")}),
             clocks=clocks, gpu_launches=((6 + 1) * world if args.ring else 6 * groups + 4) * args.steps)))
-    dist.destroy_process_group()
+    if world > 1:
+        dist.destroy_process_group()
 
 
 # --------------------------------------------------------------------------------------------------
@@ -210,7 +324,8 @@ def main():
     ap.add_argument("--workload", default="c2_hd128_32k", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="sage3_b200", choices=["sage3_b200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=4)
-    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle legs (cpu_baseline and the parity check)")
+    ap.add_argument("--no-ulysses", action="store_true", help="skip the sequence-parallel arm of the default line")
     ap.add_argument("--ulysses", action="store_true",
                     help="strong scaling: the workload's tokens are sharded over the ranks (all-to-all before and after attention)")
     ap.add_argument("--ring", action="store_true", help="with --ulysses: ring attention instead of the all-to-all exchange")
@@ -247,32 +362,13 @@ def main():
             os.dup2(saved_stdout, 1)
             os.close(saved_stdout)
 
-    # seeded synthetic input, generated on the device in chunks (the full tensors are several GB)
-    g = torch.Generator(device=dev).manual_seed(2000 + rank)
     B, Hq, Hkv, Nq, Nk, D = (w[k_] for k_ in ("B", "Hq", "Hkv", "Nq", "Nk", "D"))
     if args.ulysses:
-        if Nq % world or Nk % world or Hq % world or Hkv % world or w["causal"]:
-            raise SystemExit("--ulysses needs token and head counts divisible by the number of GPUs and a non-causal workload")
-        Nq, Nk = Nq // world, Nk // world       # this rank's token shard
-    shp_q = (B, Hq, Nq, D) if w["layout"] == "HND" else (B, Nq, Hq, D)
-    shp_k = (B, Hkv, Nk, D) if w["layout"] == "HND" else (B, Nk, Hkv, D)
-    q = torch.empty(shp_q, dtype=torch.bfloat16, device=dev).normal_(generator=g)
-    k = torch.empty(shp_k, dtype=torch.bfloat16, device=dev).normal_(generator=g)
-    v = torch.empty(shp_k, dtype=torch.bfloat16, device=dev).normal_(generator=g)
-    off_std = w["inp"].get("k_offset_std", 0.0)
-    if off_std:
-        off_shape = (B, Hkv, 1, D) if w["layout"] == "HND" else (B, 1, Hkv, D)
-        k += (off_std * torch.randn(off_shape, device=dev, generator=g)).to(torch.bfloat16)
-    if w["inp"].get("k_outlier_channels"):
-        idx = torch.randperm(D, device=dev, generator=g)[: w["inp"]["k_outlier_channels"]]
-        k[..., idx] *= 2
-    # (RoPE of the Llama-shaped workload changes values, not shapes or timing; the parity tests cover it.)
-
+        run_ulysses(args, w, rank, world, local, dev)
+        return
+    q, k, v = make_inputs_on_device(w, dev, 2000 + rank)
     flops = flops_of(w)
     stream = torch.cuda.current_stream()
-    if args.ulysses and world > 1:
-        run_ulysses(args, w, q, k, v, flops, rank, world, local, dev)
-        return
     prob = Sage3Problem(q, k, v, tensor_layout=w["layout"], is_causal=w["causal"])
 
     def step(ev=None):
@@ -316,6 +412,13 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms, pre_ms, att_ms = t.tolist()
 
+    # the output of the last timed step, for the parity check below (one head's worth of rows goes to the host)
+    parity_in = None
+    if rank == 0 and not args.no_cpu_baseline:
+        hnd = (lambda t_: t_) if w["layout"] == "HND" else (lambda t_: t_.transpose(1, 2))
+        group = Hq // Hkv
+        parity_in = tuple(hnd(t_)[:1, :n_].contiguous().cpu() for t_, n_ in ((q, group), (k, 1), (v, 1), (prob.out, group)))
+
     # end to end through the public call: pinned host tensors in, host tensor out, copies inside the timed region
     e2e = None
     if args.e2e_steps > 0:
@@ -326,7 +429,7 @@ def main():
 
         def e2e_step():
             # the public call for host-resident operands: copies in, pre-pass, attention and copy out, pipelined
-            # over (batch, kv-head) chunks
+            # over (batch, kv-head) chunks; it returns when the result is in host memory
             sageattn3_offload(qh, kh, vh, out=oh, tensor_layout=w["layout"], is_causal=w["causal"], device=dev)
 
         for _ in range(3):          # warm-up: allocator, pinned pages, clocks
@@ -348,6 +451,20 @@ def main():
         nbytes = lambda t_: t_.numel() * t_.element_size()
         e2e = dict(value=world * flops / (e2e_ms * 1e-3) / 1e12, unit="TOPS", ms_per_step=e2e_ms,
                    h2d_bytes_per_step=world * (nbytes(qh) + nbytes(kh) + nbytes(vh)), d2h_bytes_per_step=world * nbytes(oh))     # whole job
+        del qh, kh, vh, oh
+        from sageattention_b200 import sageattn3_offload_release
+        sageattn3_offload_release()
+    else:
+        del prob
+    del q, k, v
+    torch.cuda.empty_cache()
+
+    # strong-scaling arm (sequence parallel) on the two long-sequence video workloads, every rank takes part
+    ulysses = None
+    if args.workload == "c2_hd128_32k" and not args.no_ulysses:
+        ulysses = {}
+        for name, n_steps in (("c4_hunyuan", 5), ("c3_cogvideox", 10)):
+            ulysses[name] = time_sequence_parallel(name, n_steps, 3, rank, world, dev)
 
     if rank != 0:
         if world > 1:
@@ -358,13 +475,13 @@ def main():
     ms_per_step = total_ms / args.steps
     att_tops = flops / (att_ms * 1e-3) / 1e12
     fp4_peak = 4.0 * peaks["bf16_sustained"]          # dense FP4 is 4x dense bf16 on this part
-    # DRAM traffic of one attention launch: ncu measured 159.6 MB (dram__bytes_read.sum + dram__bytes_write.sum) on
-    # the ncu_small case (16 heads x 16384 tokens, D=128; profiles/attn_fwd_kernel__ncu_small.md); the kernel reads
-    # each head's operands once from DRAM and writes its output once, so traffic scales with B*H*N*D.
+    # DRAM traffic of one attention launch: a constant taken from one stored ncu capture of the small profiling case
+    # (16 heads x 16384 tokens, D = 128: 159.6 MB = dram__bytes_read.sum + dram__bytes_write.sum), scaled by B*H*N; the
+    # kernel reads each head's operands once from DRAM and writes its output once, so its traffic grows in that proportion.
     traffic, traffic_src = None, None
     if D == 128 and not w["causal"]:
         traffic = 159.6e6 * (B * Hq * Nq) / (16 * 16384.0)
-        traffic_src = "scaled from one ncu capture of the ncu_small case in proportion to B*H*N"
+        traffic_src = "constant from a stored ncu capture of a smaller case (not measured in this run), scaled in proportion to B*H*N"
     line = dict(
         metric="attention TOPS (4*B*H*Nq*Nk*D/t) of the smooth+NVFP4-quantize+attend path", value=world * flops / (ms_per_step * 1e-3) / 1e12,
         unit="TOPS", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=ms_per_step, higher_is_better=True,
@@ -378,20 +495,11 @@ def main():
         roofline=dict(bound="tensor", kernel="attn_fwd_kernel", achieved=att_tops, peak=fp4_peak, unit="TFLOP/s", frac=att_tops / fp4_peak,
                       traffic=traffic, traffic_source=traffic_src, peak_source=f"4 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']})",
                       frac_of_nominal_fp4=att_tops / NOMINAL_FP4_TFLOPS),
-        clocks=clocks, e2e=e2e, gpu_launches=6 * args.steps,
+        clocks=clocks, e2e=e2e, gpu_launches=6 * args.steps, ulysses=ulysses,
     )
     if not args.no_cpu_baseline:
-        cores = os.cpu_count() or 1
-        torch.set_num_threads(cores)
-        tot_f = tot_t = 0.0
-        desc = ""
-        t_start = time.perf_counter()
-        while time.perf_counter() - t_start < 12.0:
-            f, dt, desc = cpu_reference_sample(w)
-            tot_f += f
-            tot_t += dt
-        line["cpu_baseline"] = dict(value=tot_f / tot_t / 1e12, unit="TOPS", cores=cores, kind="port",
-                                    sample=f"{desc}; repeated for {tot_t:.1f} s")
+        line["parity"] = parity_of_timed_output(w, *parity_in)
+        line["cpu_baseline"] = cpu_baseline_report(w, os.cpu_count() or 1)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

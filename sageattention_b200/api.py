@@ -175,10 +175,87 @@ def sageattn3(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: 
         raise NotImplementedError("attn_mask is not supported by the FP4 attention path")
     if sm_scale is None and kwargs.get("scale") is not None:
         sm_scale = kwargs["scale"]          # F.scaled_dot_product_attention's name for the same thing
+    if torch.compiler.is_compiling():
+        # under torch.compile the call is one opaque operator (registered below) instead of a graph break
+        scale_f = None if isinstance(sm_scale, torch.Tensor) or sm_scale is None else float(sm_scale)
+        scale_t = sm_scale if isinstance(sm_scale, torch.Tensor) else None
+        if return_lse:
+            return torch.ops.sageattention_b200.fwd_lse(q, k, v, tensor_layout, bool(is_causal), scale_f, scale_t, bool(per_block_mean))
+        return torch.ops.sageattention_b200.fwd(q, k, v, tensor_layout, bool(is_causal), scale_f, scale_t, bool(per_block_mean))
+    if workspace is None and q.is_cuda:
+        workspace = _cached_workspace(q, k, tensor_layout, per_block_mean)
     prob = Sage3Problem(q, k, v, tensor_layout, is_causal, sm_scale, per_block_mean, workspace=workspace,
                         return_lse=return_lse)
     out = prob.run()
     return (out, prob.lse) if return_lse else out
+
+
+# ------------------------------------------------------------------------------------------------------
+# workspace cache of the functional entry points
+# ------------------------------------------------------------------------------------------------------
+# One workspace per (device, stream), grown on demand and reused by later calls: kernels of successive calls on one
+# stream run in order, so they may share it; calls on different streams get different buffers.  (Allocating 3.4 GB anew
+# on every call of the benchmark shape costs more than the pre-pass.)  Sage3Problem users manage their own.
+_WORKSPACES: dict = {}
+
+
+def _cached_workspace(q: torch.Tensor, k: torch.Tensor, tensor_layout: str, per_block_mean: bool) -> torch.Tensor:
+    hd, nd = (1, 2) if tensor_layout == "HND" else (2, 1)
+    d = _cabi.Sage3Desc()
+    d.B, d.Hq, d.Hkv, d.Nq, d.Nk, d.D = q.shape[0], q.shape[hd], k.shape[hd], q.shape[nd], k.shape[nd], q.shape[3]
+    d.dtype = _DTYPES.get(q.dtype, _cabi.SAGE3_BF16)
+    d.per_block_mean = int(bool(per_block_mean))
+    need = _cabi.lib().sage3_workspace_bytes(C.byref(d))      # 0 for an invalid shape: Sage3Problem reports it properly
+    key = (q.device.index, torch.cuda.current_stream(q.device).cuda_stream)
+    buf = _WORKSPACES.get(key)
+    if buf is None or buf.numel() < need + 256:
+        _WORKSPACES.pop(key, None)
+        buf = torch.empty(need + 256, dtype=torch.uint8, device=q.device)
+        _WORKSPACES[key] = buf
+    return buf
+
+
+def release_workspaces() -> None:
+    """Drops the workspaces that sageattn3 / sageattn / sageattn_varlen keep between calls."""
+    _WORKSPACES.clear()
+
+
+# ------------------------------------------------------------------------------------------------------
+# torch.library registration: lets torch.compile trace through the call (the reference registers its v2 kernels the
+# same way: sageattention/sm89_compile.py:5-23, 69-101 -- a custom op plus a fake implementation that only
+# describes the output)
+# ------------------------------------------------------------------------------------------------------
+def _op_impl(q, k, v, tensor_layout, is_causal, sm_scale, sm_scale_per_head, per_block_mean, return_lse):
+    scale = sm_scale_per_head if sm_scale_per_head is not None else sm_scale
+    prob = Sage3Problem(q, k, v, tensor_layout, is_causal, scale, per_block_mean,
+                        workspace=_cached_workspace(q, k, tensor_layout, per_block_mean), return_lse=return_lse)
+    out = prob.run()
+    return (out, prob.lse) if return_lse else out
+
+
+@torch.library.custom_op("sageattention_b200::fwd", mutates_args=(), device_types="cuda")
+def _fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str, is_causal: bool,
+            sm_scale: float | None, sm_scale_per_head: torch.Tensor | None, per_block_mean: bool) -> torch.Tensor:
+    return _op_impl(q, k, v, tensor_layout, is_causal, sm_scale, sm_scale_per_head, per_block_mean, False)
+
+
+@_fwd_op.register_fake
+def _(q, k, v, tensor_layout, is_causal, sm_scale, sm_scale_per_head, per_block_mean):
+    return torch.empty(q.shape, dtype=q.dtype, device=q.device)
+
+
+@torch.library.custom_op("sageattention_b200::fwd_lse", mutates_args=(), device_types="cuda")
+def _fwd_lse_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str, is_causal: bool,
+                sm_scale: float | None, sm_scale_per_head: torch.Tensor | None,
+                per_block_mean: bool) -> tuple[torch.Tensor, torch.Tensor]:
+    return _op_impl(q, k, v, tensor_layout, is_causal, sm_scale, sm_scale_per_head, per_block_mean, True)
+
+
+@_fwd_lse_op.register_fake
+def _(q, k, v, tensor_layout, is_causal, sm_scale, sm_scale_per_head, per_block_mean):
+    hd, nd = (1, 2) if tensor_layout == "HND" else (2, 1)
+    return (torch.empty(q.shape, dtype=q.dtype, device=q.device),
+            torch.empty(q.shape[0], q.shape[hd], q.shape[nd], dtype=torch.float32, device=q.device))
 
 
 def sageattn3_blackwell(q, k, v, attn_mask=None, is_causal=False, per_block_mean=True, **kwargs):
@@ -215,8 +292,10 @@ def sageattn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlen
         if k1 == k0:
             out[q0:q1].zero_()
             continue
-        prob = Sage3Problem(q[q0:q1].unsqueeze(0), k[k0:k1].unsqueeze(0), v[k0:k1].unsqueeze(0), "NHD", is_causal, sm_scale,
-                            kwargs.get("per_block_mean", True), out=out[q0:q1].unsqueeze(0))
+        qi, ki, vi = q[q0:q1].unsqueeze(0), k[k0:k1].unsqueeze(0), v[k0:k1].unsqueeze(0)
+        pbm = kwargs.get("per_block_mean", True)
+        prob = Sage3Problem(qi, ki, vi, "NHD", is_causal, sm_scale, pbm, out=out[q0:q1].unsqueeze(0),
+                            workspace=_cached_workspace(qi, ki, "NHD", pbm))
         prob.run()
     return out
 
@@ -239,7 +318,8 @@ def sageattn3_offload_release() -> None:
 
 def sageattn3_offload(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor | None = None,
                       tensor_layout: str = "HND", is_causal: bool = False, sm_scale=None, per_block_mean: bool = True,
-                      device: torch.device | str | None = None, kv_heads_per_chunk: int | None = None) -> torch.Tensor:
+                      device: torch.device | str | None = None, kv_heads_per_chunk: int | None = None,
+                      non_blocking: bool = False) -> torch.Tensor:
     """sageattn3 for operands that live in host memory (use pinned tensors): q, k, v are CPU tensors, the result
     is a CPU tensor (pinned when allocated here).
 
@@ -247,8 +327,13 @@ def sageattn3_offload(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: to
     while one chunk is being computed, the next one is copied in and the previous result is copied out.  Device
     memory holds two chunks at a time, so the host tensors may be larger than the GPU; the chunk buffers and
     streams are kept for the next call of the same shape (`sageattn3_offload_release()` drops them).  The caller's current
-    stream orders the call as a whole (it is waited for at entry and waits for the last copy at exit; the host
-    is not blocked).  A scalar or None `sm_scale` only.
+    stream orders the call as a whole (it is waited for at entry and waits for the last copy at exit).  A scalar or None
+    `sm_scale` only.
+
+    HOST SYNCHRONIZATION.  The copies run on side streams.  By default the function returns only after the last
+    device-to-host copy has completed, so `out` can be read and q, k, v reused at once.  With `non_blocking=True`
+    it returns as soon as everything is enqueued: then neither `out` may be read nor q, k, v modified on the host
+    until the caller's current stream (which waits for the last copy) has been synchronized.
     """
     if any(t.is_cuda for t in (q, k, v)):
         raise ValueError("sageattn3_offload takes host tensors; call sageattn3 for CUDA tensors")
@@ -328,4 +413,8 @@ def sageattn3_offload(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: to
     for ev in out_done:
         if ev is not None:
             cur.wait_event(ev)
+    if not non_blocking:
+        for ev in out_done:
+            if ev is not None:
+                ev.synchronize()
     return out

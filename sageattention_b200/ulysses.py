@@ -114,7 +114,8 @@ def unpack_tokens_after_exchange(recv: torch.Tensor) -> torch.Tensor:
 # ------------------------------------------------------------------------------------------------------
 def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
                       is_causal: bool = False, group: dist.ProcessGroup | None = None,
-                      attn_fn: Callable | None = None, overlap_groups: int | None = None, **kwargs) -> torch.Tensor:
+                      attn_fn: Callable | None = None, overlap_groups: int | None = None,
+                      profile: list | None = None, **kwargs) -> torch.Tensor:
     """Sequence-parallel attention.  Every rank passes its contiguous token shard
     [rank * N/P, (rank + 1) * N/P) of all heads and gets the output for the same shard.
 
@@ -127,7 +128,16 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_
     all-to-all of slice g + 1 and the return all-to-all of slice g - 1 run on NCCL's stream while slice g is
     in the pre-pass and attention kernels.  The default is one slice: on NVSwitch the exchange is a few per cent
     of a step, and at two GPUs three slices measured 3 % slower than one (more, smaller launches).
+
+    `profile`: a list that receives (name, CUDA event) pairs recorded on the current stream at the phase boundaries of
+    a one-slice call ("start", "exchanged_in", "attended", "exchanged_out"), for a time split; None in normal use.
     """
+    def mark(name):
+        if profile is not None and q.is_cuda:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(torch.cuda.current_stream(q.device))
+            profile.append((name, ev))
+
     if attn_fn is None:
         from .api import sageattn3 as attn_fn
     world = dist.get_world_size(group)
@@ -145,6 +155,7 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_
     G = max(1, min(G, hkv_l))
     bounds = [(g * hkv_l) // G for g in range(G + 1)]      # slices of the local kv heads
     q5, k5, v5 = (t.reshape(B, world, -1, n, D) for t in (qh, kh, vh))   # [B, dest rank, its heads, n, D]
+    mark("start")
     works_in, recvs = [], []
     for g in range(G):
         a, b_ = bounds[g], bounds[g + 1]
@@ -159,13 +170,16 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_
         a, b_ = bounds[g], bounds[g + 1]
         works_in[g].wait()
         ql, kl, vl = unpack_heads_after_exchange(recvs[g][0], (b_ - a) * rep, b_ - a)
+        mark("exchanged_in")
         ol = attn_fn(ql.contiguous(), kl.contiguous(), vl.contiguous(), tensor_layout="HND", is_causal=is_causal, **kwargs)
+        mark("attended")
         send_o = pack_tokens_for_exchange(ol, world)
         recv_o = torch.empty_like(send_o)
         works_out.append((dist.all_to_all_single(recv_o, send_o, group=group, async_op=True), recv_o, send_o, a, b_))
     for work, recv_o, _send_o, a, b_ in works_out:
         work.wait()
         _regroup(out5[:, :, a * rep:b_ * rep], recv_o.permute(1, 0, 2, 3, 4))     # [B, source rank, its slice of heads, n, D]
+    mark("exchanged_out")
     o = out5.reshape(B, Hq, n, D)
     return o if tensor_layout == "HND" else o.transpose(1, 2)
 

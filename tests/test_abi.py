@@ -64,6 +64,7 @@ def test_ragged_and_global_mean_layout():
 @pytest.mark.parametrize("kw,code", [
     (dict(D=96), -2), (dict(D=256), -2), (dict(Hq=3, Hkv=2), -2), (dict(Nq=0), -2), (dict(B=-1), -2),
     (dict(dtype=7), -3), (dict(Nk=1 << 25), -8),
+    (dict(B=2048, Hq=64, Hkv=64, Nq=128, Nk=128), -8),          # B * Hq beyond the 65535 (batch, head) slabs of a launch
 ])
 def test_validation_codes(kw, code):
     lib = _cabi.lib()

@@ -110,6 +110,27 @@ def test_bounded_wait_reports_instead_of_hanging(cuda_device):
     assert torch.isfinite(out.float()).all()
 
 
+def test_prepass_report_survives_the_attention_launch(cuda_device):
+    """A wait the pre-pass gave up on must still be reported after the attention launch of the same call: the two stages
+    own one half of the status words each, and an attention launch that finds the pre-pass word set does nothing."""
+    import ctypes as C
+    from sageattention_b200 import _cabi
+    q, k, v = (t.to(cuda_device) for t in O.make_inputs(1, 2, 2, 256, 256, 64, seed=5))
+    prob = Sage3Problem(q, k, v)
+    prob.prepass()
+    torch.cuda.synchronize()
+    prob.ws.buf[prob.ws.layout.status: prob.ws.layout.status + 4].view(torch.int32).fill_(116)    # as quant_k_delta_kernel would
+    prob.out.fill_(7.0)
+    prob.attention()
+    with pytest.raises(_cabi.Sage3Error) as e:
+        prob.check_status()
+    assert "116" in str(e.value)
+    assert (prob.out == 7.0).all()                       # no CTA touched the output
+    ref = prob.run().clone()                              # the next full call starts clean
+    assert prob.check_status() == 0
+    assert O.cosine(ref.cpu(), O.sageattn3_oracle(q.cpu(), k.cpu(), v.cpu())) >= COS_MIN
+
+
 @pytest.mark.parametrize("layout,causal", [("HND", False), ("NHD", True)])
 def test_offload_matches_device_call(cuda_device, layout, causal):
     """Host-resident operands, pipelined over (batch, kv-head) chunks: same bits as the all-on-device call."""
