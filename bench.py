@@ -230,13 +230,15 @@ def make_inputs_on_device(w, dev, seed, Nq=None, Nk=None):
     return q, k, v
 
 
-def time_sequence_parallel(name, steps, warmup, rank, world, dev, ring=False, overlap_groups=1):
+def time_sequence_parallel(name, steps, warmup, rank, world, dev, ring=False, overlap_groups=1, peer=False):
     """Strong-scaling arm on workload `name`: every rank holds the token shard [rank N/P, (rank + 1) N/P) of all heads;
-    one step = all-to-all, pre-pass, attention, all-to-all (at one GPU: the plain call).  Device time, max over ranks."""
+    one step = exchange, pre-pass, attention, exchange (at one GPU: the plain call).  The exchange is NCCL all-to-alls
+    (`ulysses_attention`) or, with `peer`, direct loads and stores in the other ranks' buffers (`PeerUlysses`).
+    Device time, max over ranks."""
     import torch
     import torch.distributed as dist
     from sageattention_b200 import sageattn3
-    from sageattention_b200.ulysses import ring_attention, ulysses_attention
+    from sageattention_b200.ulysses import PeerUlysses, ring_attention, ulysses_attention
     w = WORKLOADS[name]
     if w["Nq"] % world or w["Hq"] % world or w["Hkv"] % world or w["causal"]:
         return dict(skipped=f"token / head counts of {name} are not divisible by {world} GPUs")
@@ -244,9 +246,15 @@ def time_sequence_parallel(name, steps, warmup, rank, world, dev, ring=False, ov
     stream = torch.cuda.current_stream()
     prof = []
 
+    pu = None
+    if peer and world > 1:
+        pu = PeerUlysses(w["B"], w["Hq"], w["Hkv"], w["Nq"] // world, w["D"], torch.bfloat16, device=dev)
+
     def step(profile=None):
         if world == 1:
             return sageattn3(q, k, v, tensor_layout=w["layout"])
+        if pu is not None:
+            return pu(q, k, v)
         if ring:
             return ring_attention(q, k, v, tensor_layout=w["layout"])
         return ulysses_attention(q, k, v, tensor_layout=w["layout"], overlap_groups=overlap_groups, profile=profile)
@@ -264,7 +272,7 @@ def time_sequence_parallel(name, steps, warmup, rank, world, dev, ring=False, ov
     torch.cuda.synchronize()
     ms = a.elapsed_time(b_) / steps
     split = None
-    if world > 1 and not ring:
+    if world > 1 and not ring and pu is None:
         step(prof)                                   # one more step with phase marks, outside the timed region
         torch.cuda.synchronize()
         ev = dict(prof)
@@ -278,11 +286,14 @@ def time_sequence_parallel(name, steps, warmup, rank, world, dev, ring=False, ov
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = t.item()
+    if pu is not None:
+        pu.close()
     del q, k, v
     torch.cuda.empty_cache()
     res = dict(tops=flops_of(w) / (ms * 1e-3) / 1e12, ms_per_step=ms, steps=steps, scaling="strong",
                tokens_per_rank=w["Nq"] // world, heads_per_rank=w["Hq"] // world,
                sharding=("one GPU: plain call" if world == 1 else
+                         "ulysses sequence parallel, peer to peer: shards read and written in place over NVLink, two barriers" if pu is not None else
                          "ring attention (NCCL send/recv of K/V shards, LSE merge)" if ring else
                          "ulysses sequence parallel: NCCL all-to-all before and after attention"))
     if split:
@@ -298,7 +309,7 @@ def run_ulysses(args, w, rank, world, local, dev):
     if rank == 0:
         sampler.start()
     res = time_sequence_parallel(args.workload, args.steps, args.warmup, rank, world, dev, ring=args.ring,
-                                 overlap_groups=max(1, args.overlap_groups))
+                                 overlap_groups=max(1, args.overlap_groups), peer=args.peer)
     clocks = sampler.stop() if rank == 0 else None
     if rank == 0:
         if "skipped" in res:
@@ -329,6 +340,7 @@ def main():
     ap.add_argument("--ulysses", action="store_true",
                     help="strong scaling: the workload's tokens are sharded over the ranks (all-to-all before and after attention)")
     ap.add_argument("--ring", action="store_true", help="with --ulysses: ring attention instead of the all-to-all exchange")
+    ap.add_argument("--peer", action="store_true", help="with --ulysses: peer-to-peer exchange (PeerUlysses) instead of NCCL all-to-alls")
     ap.add_argument("--overlap-groups", type=int, default=0,
                     help="with --ulysses: head slices whose all-to-all overlaps the kernels of the others (0 = one slice, no overlap)")
     args = ap.parse_args()
@@ -464,7 +476,13 @@ def main():
     if args.workload == "c2_hd128_32k" and not args.no_ulysses:
         ulysses = {}
         for name, n_steps in (("c4_hunyuan", 5), ("c3_cogvideox", 10)):
-            ulysses[name] = time_sequence_parallel(name, n_steps, 3, rank, world, dev)
+            res = time_sequence_parallel(name, n_steps, 3, rank, world, dev)
+            if world > 1 and "skipped" not in res:
+                # both transports; the headline of the arm is the faster one, the other is kept beside it
+                res_p = time_sequence_parallel(name, n_steps, 3, rank, world, dev, peer=True)
+                best, other = (res_p, res) if res_p["tops"] >= res["tops"] else (res, res_p)
+                res = dict(best, other_transport=other)
+            ulysses[name] = res
 
     if rank != 0:
         if world > 1:

@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define SAGE3_ABI_VERSION 2
+#define SAGE3_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define SAGE3_API __attribute__((visibility("default")))
@@ -122,6 +122,48 @@ SAGE3_API int sage3_prepass(const Sage3Desc* desc, const void* q, const void* k,
  * sageattention/core.py:327 does for its kernels (-inf for a row without visible keys).
  */
 SAGE3_API int sage3_attn_fwd(const Sage3Desc* desc, void* ws, void* out, float* lse, void* stream);
+
+/*
+ * sage3_prepass with the K mean supplied by the caller: `km` is a device array dtype[B][Hkv][D] that is used instead of
+ * the mean over this call's Nk tokens.  For context-parallel callers whose K is one shard of a longer sequence: they
+ * pass the mean over all shards, so every shard is smoothed exactly as the whole sequence would be (api.py:84 takes
+ * the mean over the whole sequence).
+ */
+SAGE3_API int sage3_prepass_kmean(const Sage3Desc* desc, const void* q, const void* k, const void* v, const void* km, void* ws,
+                                  void* stream);
+
+/*
+ * A tensor whose token dimension is split into `parts` equal pieces that live in different buffers: piece p holds tokens
+ * [p * rows_per_part, (p + 1) * rows_per_part) and is addressed with the (b, h, n) strides of Sage3Desc, n counted from
+ * the start of the piece.  The buffers may be memory of other GPUs of the node mapped into this process (see
+ * sage3_shared_open): the kernels touch them with plain loads and stores only.  This is the peer-to-peer form of the
+ * sequence-parallel exchange that the reference leaves to xfuser (example/parallel_sageattn_cogvideo.py:8-14, 89-95):
+ * every rank's token shard stays where it is, the pre-pass of the rank that owns a head reads it from there, and the
+ * attention epilogue writes each output row into the shard of the rank that owns the token.
+ */
+#define SAGE3_MAX_PARTS 8
+typedef struct Sage3Parts {
+    int32_t parts;                  /* 1 .. SAGE3_MAX_PARTS */
+    int32_t rows_per_part;          /* tokens per piece; parts * rows_per_part >= the tensor's token count */
+    void* base[SAGE3_MAX_PARTS];    /* 16-byte aligned; base[p] already points at this call's first (batch, head) */
+} Sage3Parts;
+
+/* sage3_prepass / sage3_attn_fwd on token-split tensors.  No counterpart in the reference. */
+SAGE3_API int sage3_prepass_parts(const Sage3Desc* desc, const Sage3Parts* q, const Sage3Parts* k, const Sage3Parts* v, void* ws,
+                                  void* stream);
+SAGE3_API int sage3_attn_fwd_parts(const Sage3Desc* desc, void* ws, const Sage3Parts* out, float* lse, void* stream);
+
+/*
+ * Device memory that other processes on the same node can map (CUDA IPC), for the buffers behind Sage3Parts.
+ * sage3_shared_alloc: cudaMalloc on the current device + a 64-byte handle to pass to the other processes;
+ * sage3_shared_open: maps such a handle into this process (peer access is enabled on first use);
+ * sage3_shared_close / sage3_shared_free undo them.  The only entry points of this library that allocate.
+ * No counterpart in the reference.
+ */
+SAGE3_API int sage3_shared_alloc(size_t bytes, void** ptr, unsigned char handle[64]);
+SAGE3_API int sage3_shared_open(const unsigned char handle[64], void** ptr);
+SAGE3_API int sage3_shared_close(void* ptr);
+SAGE3_API int sage3_shared_free(void* ptr);
 
 /* sage3_prepass followed by sage3_attn_fwd on the same stream. */
 SAGE3_API int sage3_fwd(const Sage3Desc* desc, const void* q, const void* k, const void* v, void* ws, void* out,

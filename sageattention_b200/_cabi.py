@@ -12,7 +12,7 @@ _PKG = pathlib.Path(__file__).resolve().parent
 LIB_PATH = _PKG / "libsage3_b200.so"
 
 SAGE3_FP16, SAGE3_BF16 = 0, 1
-ABI_VERSION = 2          # SAGE3_ABI_VERSION of include/sage3_b200.h this module's structs were written for
+ABI_VERSION = 3          # SAGE3_ABI_VERSION of include/sage3_b200.h this module's structs were written for
 SAGE3_OK = 0
 SAGE3_E_DEVICE_WAIT = -9
 
@@ -30,6 +30,13 @@ class Sage3Workspace(C.Structure):
     _fields_ = [(n, C.c_size_t) for n in
                 ("status", "kpart", "km", "qm", "delta", "q_codes", "q_sf", "k_codes", "k_sf", "v_codes", "v_sf",
                  "qkm", "total_bytes")] + [(n, C.c_int32) for n in ("nq_pad", "nk_pad", "nqm", "kchunks")]
+
+
+MAX_PARTS = 8
+
+
+class Sage3Parts(C.Structure):
+    _fields_ = [("parts", C.c_int32), ("rows_per_part", C.c_int32), ("base", C.c_void_p * MAX_PARTS)]
 
 
 class Sage3Error(RuntimeError):
@@ -68,6 +75,20 @@ def lib() -> C.CDLL:
     l.sage3_prepass.argtypes = [P(Sage3Desc), V, V, V, V, V]
     l.sage3_attn_fwd.restype = C.c_int
     l.sage3_attn_fwd.argtypes = [P(Sage3Desc), V, V, V, V]
+    l.sage3_prepass_kmean.restype = C.c_int
+    l.sage3_prepass_kmean.argtypes = [P(Sage3Desc), V, V, V, V, V, V]
+    l.sage3_prepass_parts.restype = C.c_int
+    l.sage3_prepass_parts.argtypes = [P(Sage3Desc), P(Sage3Parts), P(Sage3Parts), P(Sage3Parts), V, V]
+    l.sage3_attn_fwd_parts.restype = C.c_int
+    l.sage3_attn_fwd_parts.argtypes = [P(Sage3Desc), V, P(Sage3Parts), V, V]
+    l.sage3_shared_alloc.restype = C.c_int
+    l.sage3_shared_alloc.argtypes = [C.c_size_t, P(C.c_void_p), C.c_char_p]
+    l.sage3_shared_open.restype = C.c_int
+    l.sage3_shared_open.argtypes = [C.c_char_p, P(C.c_void_p)]
+    l.sage3_shared_close.restype = C.c_int
+    l.sage3_shared_close.argtypes = [V]
+    l.sage3_shared_free.restype = C.c_int
+    l.sage3_shared_free.argtypes = [V]
     l.sage3_fwd.restype = C.c_int
     l.sage3_fwd.argtypes = [P(Sage3Desc), V, V, V, V, V, V, V]
     l.sage3_selftest_wait_timeout.restype = C.c_int
@@ -85,7 +106,9 @@ def lib() -> C.CDLL:
 
 
 EXPORTED = ["sage3_version", "sage3_strerror", "sage3_workspace_layout", "sage3_workspace_bytes", "sage3_prepass",
-            "sage3_attn_fwd", "sage3_fwd", "sage3_check_status", "sage3_kmean_noalloc", "sage3_selftest_wait_timeout", "sage3_slab_copy", "sage3_merge_partial"]
+            "sage3_attn_fwd", "sage3_fwd", "sage3_check_status", "sage3_kmean_noalloc", "sage3_selftest_wait_timeout", "sage3_slab_copy", "sage3_merge_partial",
+            "sage3_prepass_kmean", "sage3_prepass_parts", "sage3_attn_fwd_parts", "sage3_shared_alloc", "sage3_shared_open",
+            "sage3_shared_close", "sage3_shared_free"]
 
 
 def check(code: int, where: str) -> None:

@@ -119,6 +119,37 @@ class Sage3Problem:
         shift = (-workspace.data_ptr()) % 256
         self.ws = Workspace(workspace[shift: shift + lay.total_bytes], lay)
 
+    @classmethod
+    def for_shape(cls, B: int, Hq: int, Hkv: int, Nq: int, Nk: int, D: int, dtype: torch.dtype, device: torch.device,
+                  is_causal: bool = False, sm_scale=None, per_block_mean: bool = True, q_stride=None, k_stride=None,
+                  v_stride=None, o_stride=None) -> "Sage3Problem":
+        """A problem described by its shape alone (descriptor + workspace, no tensors): for callers that hand the
+        buffers to the library themselves, e.g. token-split buffers (`sage3_prepass_parts`).  Strides are element
+        strides for (batch, head, token); default: contiguous [B, H, N, D]."""
+        if dtype not in _DTYPES:
+            raise TypeError("dtype must be torch.float16 or torch.bfloat16")
+        if torch.cuda.get_device_capability(device) != (10, 0):
+            raise RuntimeError("sageattention_b200 runs on compute capability 10.0 (B200) only")
+        self = cls.__new__(cls)
+        self.q = self.k = self.v = self.out = self.lse = None
+        self.tensor_layout, self.device, self._scale_tensor = "HND", device, None
+        d = _cabi.Sage3Desc()
+        d.B, d.Hq, d.Hkv, d.Nq, d.Nk, d.D = B, Hq, Hkv, Nq, Nk, D
+        d.dtype = _DTYPES[dtype]
+        d.is_causal, d.per_block_mean = int(bool(is_causal)), int(bool(per_block_mean))
+        d.q_stride = (C.c_int64 * 3)(*(q_stride or (Hq * Nq * D, Nq * D, D)))
+        d.k_stride = (C.c_int64 * 3)(*(k_stride or (Hkv * Nk * D, Nk * D, D)))
+        d.v_stride = (C.c_int64 * 3)(*(v_stride or k_stride or (Hkv * Nk * D, Nk * D, D)))
+        d.o_stride = (C.c_int64 * 3)(*(o_stride or q_stride or (Hq * Nq * D, Nq * D, D)))
+        d.sm_scale = 0.0 if sm_scale is None else float(sm_scale)
+        self.desc = d
+        lay = _cabi.Sage3Workspace()
+        _cabi.check(_cabi.lib().sage3_workspace_layout(C.byref(d), C.byref(lay)), "sage3_workspace_layout")
+        workspace = torch.empty(lay.total_bytes + 256, dtype=torch.uint8, device=device)
+        shift = (-workspace.data_ptr()) % 256
+        self.ws = Workspace(workspace[shift: shift + lay.total_bytes], lay)
+        return self
+
     # -- launches -------------------------------------------------------------------------------------
     def _stream(self) -> int:
         return torch.cuda.current_stream(self.device).cuda_stream

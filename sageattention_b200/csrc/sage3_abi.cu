@@ -1,6 +1,7 @@
 // extern "C" boundary of libsage3_b200.so (declared in include/sage3_b200.h): argument validation,
 // workspace layout, and the launches.  No allocation, no caching of caller pointers, no exceptions.
 #include <cuda_runtime.h>
+#include <string.h>
 
 #include "../../include/sage3_b200.h"
 #include "sage3_common.cuh"
@@ -78,13 +79,36 @@ inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_
 // so a wait the pre-pass gave up on is still there after the attention launch (whose CTAs read it and exit at once).
 constexpr int kStatusWords = 64, kAttnStatusWord = 32;
 
-int attn_impl(const Sage3Desc* desc, void* ws, void* out, float* lse, float* debug, void* stream) {
+// checks a Sage3Parts argument and converts it; `align`: required alignment of every base pointer
+int to_parts(const Sage3Parts* in, int64_t rows_total, sage3::PartsPtr* out) {
+    if (!in) return SAGE3_E_NULL;
+    if (in->parts < 1 || in->parts > sage3::kMaxParts || in->rows_per_part <= 0) return SAGE3_E_SHAPE;
+    if ((int64_t)in->parts * in->rows_per_part < rows_total) return SAGE3_E_SHAPE;
+    *out = sage3::PartsPtr{};
+    for (int i = 0; i < in->parts; ++i) {
+        if (!in->base[i]) return SAGE3_E_NULL;
+        if (!aligned(in->base[i], 16)) return SAGE3_E_ALIGN;
+        out->base[i] = in->base[i];
+    }
+    for (int i = in->parts; i < sage3::kMaxParts; ++i) out->base[i] = in->base[in->parts - 1];
+    out->rows = in->parts == 1 ? 0 : in->rows_per_part;
+    return SAGE3_OK;
+}
+
+sage3::PartsPtr one_part(const void* p) {
+    sage3::PartsPtr r = {};
+    for (int i = 0; i < sage3::kMaxParts; ++i) r.base[i] = const_cast<void*>(p);
+    r.rows = 0;
+    return r;
+}
+
+int attn_impl(const Sage3Desc* desc, void* ws, const sage3::PartsPtr& out, float* lse, float* debug, void* stream) {
     Sage3Workspace w;
     int rc = layout(desc, &w);
     if (rc != SAGE3_OK) return rc;
-    if (!ws || !out) return SAGE3_E_NULL;
+    if (!ws || !out.base[0]) return SAGE3_E_NULL;
     if (lse != nullptr && !aligned(lse, 4)) return SAGE3_E_ALIGN;
-    if (!aligned(ws, kWsAlign) || !aligned(out, 16)) return SAGE3_E_ALIGN;
+    if (!aligned(ws, kWsAlign) || !aligned(out.base[0], 16)) return SAGE3_E_ALIGN;
     rc = check_arch();
     if (rc != SAGE3_OK) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -231,12 +255,13 @@ SAGE3_API size_t sage3_workspace_bytes(const Sage3Desc* desc) {
     return layout(desc, &w) == SAGE3_OK ? w.total_bytes : 0;
 }
 
-SAGE3_API int sage3_prepass(const Sage3Desc* desc, const void* q, const void* k, const void* v, void* ws, void* stream) {
+static int prepass_impl(const Sage3Desc* desc, const sage3::PartsPtr& q, const sage3::PartsPtr& k, const sage3::PartsPtr& v,
+                        const void* km_in, void* ws, void* stream) {
     Sage3Workspace w;
     int rc = layout(desc, &w);
     if (rc != SAGE3_OK) return rc;
-    if (!q || !k || !v || !ws) return SAGE3_E_NULL;
-    if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(ws, kWsAlign)) return SAGE3_E_ALIGN;
+    if (!ws) return SAGE3_E_NULL;
+    if (!aligned(ws, kWsAlign)) return SAGE3_E_ALIGN;
     rc = check_arch();
     if (rc != SAGE3_OK) return rc;
     uint8_t* base = static_cast<uint8_t*>(ws);
@@ -260,18 +285,87 @@ SAGE3_API int sage3_prepass(const Sage3Desc* desc, const void* q, const void* k,
     a.v_codes = base + w.v_codes; a.v_sf = base + w.v_sf;
     a.qkm = reinterpret_cast<float*>(base + w.qkm);
     a.status = reinterpret_cast<int*>(base + w.status);
-    if (cudaMemsetAsync(base + w.status, 0, kStatusWords * sizeof(int32_t), static_cast<cudaStream_t>(stream)) != cudaSuccess) return SAGE3_E_CUDA;
-    return sage3::launch_prepass(a, static_cast<cudaStream_t>(stream)) == cudaSuccess ? SAGE3_OK : SAGE3_E_CUDA;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(base + w.status, 0, kStatusWords * sizeof(int32_t), st) != cudaSuccess) return SAGE3_E_CUDA;
+    a.km_given = km_in != nullptr;
+    if (km_in != nullptr &&
+        cudaMemcpyAsync(a.km, km_in, (size_t)desc->B * desc->Hkv * desc->D * 2, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+        return SAGE3_E_CUDA;
+    return sage3::launch_prepass(a, st) == cudaSuccess ? SAGE3_OK : SAGE3_E_CUDA;
+}
+
+SAGE3_API int sage3_prepass(const Sage3Desc* desc, const void* q, const void* k, const void* v, void* ws, void* stream) {
+    if (!q || !k || !v) return SAGE3_E_NULL;
+    if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16)) return SAGE3_E_ALIGN;
+    return prepass_impl(desc, one_part(q), one_part(k), one_part(v), nullptr, ws, stream);
+}
+
+SAGE3_API int sage3_prepass_kmean(const Sage3Desc* desc, const void* q, const void* k, const void* v, const void* km, void* ws,
+                                  void* stream) {
+    if (!q || !k || !v || !km) return SAGE3_E_NULL;
+    if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(km, 2)) return SAGE3_E_ALIGN;
+    return prepass_impl(desc, one_part(q), one_part(k), one_part(v), km, ws, stream);
+}
+
+SAGE3_API int sage3_prepass_parts(const Sage3Desc* desc, const Sage3Parts* q, const Sage3Parts* k, const Sage3Parts* v, void* ws,
+                                  void* stream) {
+    if (!desc) return SAGE3_E_NULL;
+    sage3::PartsPtr qp, kp, vp;
+    int rc = to_parts(q, desc->Nq, &qp);
+    if (rc == SAGE3_OK) rc = to_parts(k, desc->Nk, &kp);
+    if (rc == SAGE3_OK) rc = to_parts(v, desc->Nk, &vp);
+    if (rc != SAGE3_OK) return rc;
+    return prepass_impl(desc, qp, kp, vp, nullptr, ws, stream);
+}
+
+SAGE3_API int sage3_attn_fwd_parts(const Sage3Desc* desc, void* ws, const Sage3Parts* out, float* lse, void* stream) {
+    if (!desc) return SAGE3_E_NULL;
+    sage3::PartsPtr op;
+    const int rc = to_parts(out, desc->Nq, &op);
+    if (rc != SAGE3_OK) return rc;
+    return attn_impl(desc, ws, op, lse, nullptr, stream);
+}
+
+// ---- memory that other processes of the node can map (for the peer-to-peer form of sequence parallelism) ----------
+SAGE3_API int sage3_shared_alloc(size_t bytes, void** ptr, unsigned char handle[64]) {
+    if (!ptr || !handle || bytes == 0) return SAGE3_E_NULL;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    if (cudaMalloc(ptr, bytes) != cudaSuccess) return SAGE3_E_CUDA;
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, *ptr) != cudaSuccess) {
+        cudaFree(*ptr);
+        *ptr = nullptr;
+        return SAGE3_E_CUDA;
+    }
+    memcpy(handle, &h, 64);
+    return SAGE3_OK;
+}
+
+SAGE3_API int sage3_shared_open(const unsigned char handle[64], void** ptr) {
+    if (!ptr || !handle) return SAGE3_E_NULL;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    return cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess ? SAGE3_OK : SAGE3_E_CUDA;
+}
+
+SAGE3_API int sage3_shared_close(void* ptr) {
+    if (!ptr) return SAGE3_E_NULL;
+    return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? SAGE3_OK : SAGE3_E_CUDA;
+}
+
+SAGE3_API int sage3_shared_free(void* ptr) {
+    if (!ptr) return SAGE3_E_NULL;
+    return cudaFree(ptr) == cudaSuccess ? SAGE3_OK : SAGE3_E_CUDA;
 }
 
 SAGE3_API int sage3_attn_fwd(const Sage3Desc* desc, void* ws, void* out, float* lse, void* stream) {
-    return attn_impl(desc, ws, out, lse, nullptr, stream);
+    return attn_impl(desc, ws, one_part(out), lse, nullptr, stream);
 }
 
 #ifdef SAGE3_DEV_TRACE
 // development builds only (not declared in the public header): attention with the instrumentation dump
 SAGE3_API int sage3_attn_fwd_debug(const Sage3Desc* desc, void* ws, void* out, float* debug, void* stream) {
-    return attn_impl(desc, ws, out, nullptr, debug, stream);
+    return attn_impl(desc, ws, one_part(out), nullptr, debug, stream);
 }
 #endif
 

@@ -70,7 +70,8 @@ struct AttnParams {
     const float* sm_scale_per_head;
     const uint8_t *q_sf, *k_sf, *v_sf;
     const uint16_t* delta;              // 16-bit elements [B*Hq][nqm][nkb*128]
-    void* out;
+    void* out[kMaxParts];               // output buffers; out_rows == 0: one buffer
+    int out_rows;                       // query rows per output part (rows of one (batch, head) go to part row / out_rows)
     int64_t os0, os1, os2;
     float* lse;                         // optional fp32 [B*Hq][Nq]
     const float* qkm;                   // fp32 [B*Hq][nqt*128]: q . km per query row
@@ -543,7 +544,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
             if (alive) {
                 const float inv_l = (l_tot == 0.f || l_tot != l_tot) ? 0.f : __frcp_rn(l_tot);
-                OutT* orow = static_cast<OutT*>(p.out) + b * p.os0 + hq * p.os1 + (int64_t)grow * p.os2 + (D / 2) * h;
+                // the row's home: one output buffer, or the part that owns this token (another GPU's memory when the
+                // output goes straight back to the token shards of a sequence-parallel group: plain stores)
+                const int opart = (p.out_rows == 0) ? 0 : min(grow / p.out_rows, kMaxParts - 1);
+                const int orow_l = grow - opart * p.out_rows;
+                OutT* orow = static_cast<OutT*>(p.out[opart]) + b * p.os0 + hq * p.os1 + (int64_t)orow_l * p.os2 + (D / 2) * h;
 #pragma unroll
                 for (int cc = 0; cc < D / 64; ++cc) {
                     float o[32];
@@ -653,7 +658,8 @@ cudaError_t launch_attn(const AttnArgs& a, cudaStream_t st, int* driver_rc) {
     p.sm_scale_per_head = a.sm_scale_per_head;
     p.q_sf = a.q_sf; p.k_sf = a.k_sf; p.v_sf = a.v_sf;
     p.delta = static_cast<const uint16_t*>(a.delta);
-    p.out = a.out;
+    for (int i = 0; i < kMaxParts; ++i) p.out[i] = a.out.base[i];
+    p.out_rows = a.out.rows;
     p.lse = a.lse; p.qkm = a.qkm; p.sm_scale = a.sm_scale;
     p.os0 = a.os[0]; p.os1 = a.os[1]; p.os2 = a.os[2];
     p.status = a.status;

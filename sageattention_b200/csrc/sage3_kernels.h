@@ -7,12 +7,22 @@
 namespace sage3 {
 
 constexpr int kRowsPerChunk = 512;   // rows per partial column sum (fixes the summation order)
+constexpr int kMaxParts = 8;         // a tensor's tokens may be split over this many buffers (one per GPU of a node)
+
+// A tensor whose token dimension is split into equal parts living in different buffers (e.g. the token shards of the
+// ranks of a sequence-parallel group, mapped into this process): part p holds tokens [p * rows, (p + 1) * rows).
+// rows == 0: one buffer, base[0].
+struct PartsPtr {
+    void* base[kMaxParts];
+    int rows;
+};
 
 struct PrepassArgs {
-    const void *q, *k, *v;
+    PartsPtr q, k, v;
     int64_t qs[3], ks[3], vs[3];   // element strides for (b, h, n)
     int B, Hq, Hkv, Nq, Nk, D, Nq_p, Nk_p, nqm;
     int per_block_mean, is_bf16;
+    int km_given;                  // the K mean is already in `km` (computed elsewhere): skip its two kernels
     int kchunks_k, kchunks_q;
     float* kpart;
     void *km, *qm, *delta;
@@ -28,7 +38,7 @@ struct AttnArgs {
     const float* sm_scale_per_head; // device [Hq] or nullptr
     const void* delta;              // dtype [B][Hq][nqm][Nk_p]
     const uint8_t *q_codes, *q_sf, *k_codes, *k_sf, *v_codes, *v_sf;
-    void* out;
+    PartsPtr out;
     int64_t os[3];
     float* lse;                     // optional fp32 [B][Hq][Nq]; nullptr if not wanted
     const float* qkm;               // fp32 [B][Hq][Nq_p] from the pre-pass

@@ -37,6 +37,25 @@ template <> struct Num<__half> {
     }
 };
 
+// Rows of an input tensor that may be split over several buffers along the token dimension.
+template <typename T>
+struct Src {
+    const T* part[kMaxParts];
+    int rows;                       // tokens per part; 0 = everything in part[0]
+    __device__ __forceinline__ const T* row(int64_t bh_off, int r, int64_t sn) const {
+        if (rows == 0) return part[0] + bh_off + (int64_t)r * sn;
+        const int pi = min(r / rows, kMaxParts - 1);
+        return part[pi] + bh_off + (int64_t)(r - pi * rows) * sn;
+    }
+};
+template <typename T>
+static Src<T> make_src(const PartsPtr& a) {
+    Src<T> s;
+    for (int i = 0; i < kMaxParts; ++i) s.part[i] = static_cast<const T*>(a.base[i]);
+    s.rows = a.rows;
+    return s;
+}
+
 // 16 elements stay packed in two 128-bit registers until they are needed (keeps the register count, and with it
 // the number of resident CTAs, where an HBM-bound kernel needs it)
 template <typename T>
@@ -79,20 +98,20 @@ __device__ __forceinline__ void quant16(const float* x, uint32_t& lo, uint32_t& 
 // (deterministic: no atomics, the summation order depends on N only)
 // ------------------------------------------------------------------------------------------------
 template <typename T, int D>
-__global__ void __launch_bounds__(256) colsum_partial_kernel(const T* __restrict__ x, int64_t sb, int64_t sh,
+__global__ void __launch_bounds__(256) colsum_partial_kernel(const Src<T> x, int64_t sb, int64_t sh,
                                                              int64_t sn, int H, int N,
                                                              float* __restrict__ part, int chunks) {
     constexpr int TPR = D / 8;           // threads per row (8 elements = 16 bytes each)
     constexpr int RPP = 256 / TPR;       // rows per pass
     const int chunk = blockIdx.x, bh = blockIdx.y;
     const int b = bh / H, h = bh % H;
-    const T* base = x + b * sb + h * sh;
+    const int64_t bh_off = b * sb + h * sh;
     const int c8 = threadIdx.x % TPR, rl = threadIdx.x / TPR;
     const int r0 = chunk * kRowsPerChunk;
     const int r1 = min(N, r0 + kRowsPerChunk);
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int r = r0 + rl; r < r1; r += RPP) {
-        const uint4 a = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)r * sn + c8 * 8));
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(x.row(bh_off, r, sn) + c8 * 8));
         const uint32_t w[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -129,7 +148,7 @@ enum { kModeQBlockMean = 0, kModeQGlobalMean = 1 };
 
 template <typename T, int D, int MODE>
 __global__ void __launch_bounds__(256, 3) quant_rows_kernel(
-    const T* __restrict__ x, int64_t sb, int64_t sh, int64_t sn, int H, int N, int Np,
+    const Src<T> x, int64_t sb, int64_t sh, int64_t sn, int H, int N, int Np,
     const T* __restrict__ mean_in,     // one mean per head: qm [B*H][D]; unused for block mean
     T* __restrict__ qm_out,            // block mean: [B*H][Np/128][D]
     uint8_t* __restrict__ codes,       // [B*H][Np][D/2]
@@ -145,7 +164,7 @@ __global__ void __launch_bounds__(256, 3) quant_rows_kernel(
     const int b = bh / H, h = bh % H;
     const int t = threadIdx.x;
     const int c = t % CH, rl = t / CH;
-    const T* base = x + b * sb + h * sh;
+    const int64_t bh_off = b * sb + h * sh;
     const int row0 = tile * kBlock;
 
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -157,7 +176,7 @@ __global__ void __launch_bounds__(256, 3) quant_rows_kernel(
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
         const int r = row0 + rl + RPP * i;
-        load16_packed<T>(base + (int64_t)r * sn + c * 16, r < N, raw[i][0], raw[i][1]);
+        load16_packed<T>(x.row(bh_off, r, sn) + c * 16, r < N, raw[i][0], raw[i][1]);
     }
 
     // x . km of every row: 16 products per thread, then a sum over the CH neighbouring lanes that share the row
@@ -282,7 +301,7 @@ __global__ void __launch_bounds__(256, 3) quant_rows_kernel(
 // ------------------------------------------------------------------------------------------------
 template <typename T, int D>
 __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
-    const T* __restrict__ x, int64_t sb, int64_t sh, int64_t sn, int H, int N, int Np,
+    const Src<T> x, int64_t sb, int64_t sh, int64_t sn, int H, int N, int Np,
     const T* __restrict__ km,          // [B*H][D]
     uint8_t* __restrict__ codes,       // [B*H][Np][D/2]
     uint8_t* __restrict__ sfs,         // [B*H][Np/128][D/64][512]
@@ -300,7 +319,7 @@ __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
     const int b = bh / H, h = bh % H;
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int c = t % CH, rl = t / CH;
-    const T* base = x + b * sb + h * sh;
+    const int64_t bh_off = b * sb + h * sh;
     const int row0 = tile * kBlock;
 
     extern __shared__ uint8_t smem_dyn[];
@@ -327,7 +346,7 @@ __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
         const int r = row0 + rl + RPP * i;
-        load16_packed<T>(base + (int64_t)r * sn + c * 16, r < N, raw[i][0], raw[i][1]);
+        load16_packed<T>(x.row(bh_off, r, sn) + c * 16, r < N, raw[i][0], raw[i][1]);
     }
     if (t < D) s_mean[t] = Num<T>::to_f(km[(int64_t)bh * D + t]);
     tc_fence_before();
@@ -447,14 +466,14 @@ __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
 // V: one tile of 128 tokens x D channels per CTA -> V^T codes (microblocks along tokens) + scale atoms
 // ------------------------------------------------------------------------------------------------
 template <typename T, int D>
-__global__ void __launch_bounds__(256) quant_vt_kernel(const T* __restrict__ x, int64_t sb, int64_t sh, int64_t sn,
+__global__ void __launch_bounds__(256) quant_vt_kernel(const Src<T> x, int64_t sb, int64_t sh, int64_t sn,
                                                        int H, int N, int Np, uint8_t* __restrict__ codes,
                                                        uint8_t* __restrict__ sfs) {
     constexpr int PITCH = D + 2;          // elements; word pitch odd -> column reads are conflict-free
     const int tile = blockIdx.x, bh = blockIdx.y;
     const int b = bh / H, h = bh % H;
     const int t = threadIdx.x;
-    const T* base = x + b * sb + h * sh;
+    const int64_t bh_off = b * sb + h * sh;
     const int row0 = tile * kBlock;
 
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -470,7 +489,7 @@ __global__ void __launch_bounds__(256) quant_vt_kernel(const T* __restrict__ x, 
     for (int r = t / TPR; r < kBlock; r += RPP) {
         const int c8 = t % TPR;
         uint4 val = make_uint4(0, 0, 0, 0);
-        if (row0 + r < N) val = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)(row0 + r) * sn + c8 * 8));
+        if (row0 + r < N) val = __ldg(reinterpret_cast<const uint4*>(x.row(bh_off, row0 + r, sn) + c8 * 8));
         uint32_t* dst = reinterpret_cast<uint32_t*>(s_v + r * PITCH + c8 * 8);   // 4-byte aligned (PITCH even)
         dst[0] = val.x; dst[1] = val.y; dst[2] = val.z; dst[3] = val.w;
     }
@@ -512,18 +531,18 @@ __global__ void __launch_bounds__(256) quant_vt_kernel(const T* __restrict__ x, 
 // ------------------------------------------------------------------------------------------------
 template <typename T, int D>
 static cudaError_t launch_prepass_t(const PrepassArgs& a, cudaStream_t st) {
-    const T* q = static_cast<const T*>(a.q);
-    const T* k = static_cast<const T*>(a.k);
-    const T* v = static_cast<const T*>(a.v);
+    const Src<T> q = make_src<T>(a.q), k = make_src<T>(a.k), v = make_src<T>(a.v);
     T* km = static_cast<T*>(a.km);
     T* qm = static_cast<T*>(a.qm);
     T* delta = static_cast<T*>(a.delta);
     const int BHq = a.B * a.Hq, BHkv = a.B * a.Hkv;
 
-    // K mean over its Nk tokens
-    colsum_partial_kernel<T, D><<<dim3(a.kchunks_k, BHkv), 256, 0, st>>>(k, a.ks[0], a.ks[1], a.ks[2], a.Hkv, a.Nk,
-                                                                         a.kpart, a.kchunks_k);
-    colmean_finalize_kernel<T, D><<<BHkv, D, 0, st>>>(a.kpart, a.kchunks_k, 1.0f / (float)a.Nk, km);
+    // K mean over its Nk tokens (unless the caller supplied it, e.g. the mean over all shards of a longer sequence)
+    if (!a.km_given) {
+        colsum_partial_kernel<T, D><<<dim3(a.kchunks_k, BHkv), 256, 0, st>>>(k, a.ks[0], a.ks[1], a.ks[2], a.Hkv, a.Nk,
+                                                                             a.kpart, a.kchunks_k);
+        colmean_finalize_kernel<T, D><<<BHkv, D, 0, st>>>(a.kpart, a.kchunks_k, 1.0f / (float)a.Nk, km);
+    }
 
     const size_t smem_q = D * 4 + (D / 64) * 512;
     if (a.per_block_mean) {
@@ -595,8 +614,10 @@ int scratch_for_current_device(float** out) {
 template <typename T, int D>
 cudaError_t launch_kmean_t(const Sage3Desc* d, const void* k, void* km, float* scratch, int chunks, cudaStream_t st) {
     const int BH = d->B * d->Hkv;
+    sage3::PartsPtr one = {};
+    one.base[0] = const_cast<void*>(k);
     sage3::colsum_partial_kernel<T, D><<<dim3(chunks, BH), 256, 0, st>>>(
-        static_cast<const T*>(k), d->k_stride[0], d->k_stride[1], d->k_stride[2], d->Hkv, d->Nk, scratch, chunks);
+        sage3::make_src<T>(one), d->k_stride[0], d->k_stride[1], d->k_stride[2], d->Hkv, d->Nk, scratch, chunks);
     sage3::colmean_finalize_kernel<T, D><<<BH, D, 0, st>>>(scratch, chunks, 1.0f / (float)d->Nk, static_cast<T*>(km));
     return cudaGetLastError();
 }

@@ -15,7 +15,11 @@ shards (`ring_attention`): K / V shards travel around the ring while every rank 
 holds, and the partial results are merged through their log-sum-exp (the use `return_lse` exists for,
 sageattention/core.py:120-122).
 
-The exchanged tensors land in this GPU's own memory before any kernel reads them.
+With `ulysses_attention` and `ring_attention` the exchanged tensors land in this GPU's own memory (NCCL) before any
+kernel reads them.  `PeerUlysses` is the peer-to-peer form of the same exchange on one NVSwitch node: the token shards
+stay where they are, in buffers that every rank maps (CUDA IPC); the pre-pass of the rank that owns a head reads the
+shards over NVLink with plain loads, and the attention epilogue stores every output row straight into the shard of the
+rank that owns the token.  No all-to-all, no regrouping pass: two small barriers per call.
 """
 from __future__ import annotations
 
@@ -257,3 +261,158 @@ def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_lay
         if kv_next is not None:
             kv = kv_next
     return out if tensor_layout == "HND" else out.transpose(1, 2)
+
+
+# ------------------------------------------------------------------------------------------------------
+# peer-to-peer sequence parallelism (one NVSwitch node)
+# ------------------------------------------------------------------------------------------------------
+class _DeviceBytes:
+    """Lets torch wrap device memory that the library allocated (CUDA array interface, no copy)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = dict(shape=(nbytes,), typestr="|u1", data=(ptr, False), version=3)
+
+
+class PeerUlysses:
+    """Sequence-parallel attention without all-to-alls, for ranks that are GPUs of one node.
+
+    Every rank owns the token shard [rank * n, (rank + 1) * n) of all heads and computes attention for the heads
+    [rank * H / P, (rank + 1) * H / P) over all tokens, exactly as `ulysses_attention` does; the result for a rank's
+    tokens equals `ulysses_attention`'s and the single-GPU call's bit for bit.  The difference is the transport:
+
+      * q, k, v shards are copied once into buffers that all ranks have mapped (or written there by the caller in the
+        first place: `stage()` returns the views) -- barrier --
+      * the pre-pass kernels read the rows they need directly from the owners' buffers (plain loads over NVLink),
+      * the attention kernel's epilogue writes each output row directly into the output buffer of the rank that owns the
+        token (plain stores over NVLink) -- barrier --
+      * the rank returns a view of its own output buffer, [B, Hq, n, D].
+
+    Buffers come in two sets used alternately, so a call may start while a slower rank still reads the previous
+    call's buffers; the view returned by call i is overwritten by call i + 2.  Shapes are fixed at construction.
+    The barriers are one-element NCCL all-reduces on the caller's stream (the host is not blocked).
+    """
+
+    def __init__(self, B: int, Hq: int, Hkv: int, tokens_per_rank: int, D: int, dtype: torch.dtype = torch.bfloat16,
+                 group: dist.ProcessGroup | None = None, device: torch.device | None = None):
+        import ctypes as C
+        from . import _cabi
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > _cabi.MAX_PARTS:
+            raise ValueError(f"PeerUlysses supports up to {_cabi.MAX_PARTS} ranks (one node)")
+        if Hq % self.world or Hkv % self.world or Hq % Hkv:
+            raise ValueError(f"head counts ({Hq}, {Hkv}) must be multiples of the group size {self.world}")
+        self.B, self.Hq, self.Hkv, self.n, self.D, self.dtype = B, Hq, Hkv, tokens_per_rank, D, dtype
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        es = torch.empty(0, dtype=dtype).element_size()
+        self._es = es
+        q_bytes, kv_bytes = B * Hq * self.n * D * es, B * Hkv * self.n * D * es
+        # one allocation per set: [q | k | v | out]
+        self._offs = (0, q_bytes, q_bytes + kv_bytes, q_bytes + 2 * kv_bytes)
+        self._set_bytes = 2 * q_bytes + 2 * kv_bytes
+        lib = _cabi.lib()
+        self._own, handles = [], []
+        with torch.cuda.device(self.device):
+            for _ in range(2):
+                ptr, h = C.c_void_p(), C.create_string_buffer(64)
+                _cabi.check(lib.sage3_shared_alloc(self._set_bytes, C.byref(ptr), h), "sage3_shared_alloc")
+                self._own.append(ptr.value)
+                handles.append(h.raw)
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, handles, group=group)
+        self._peer = []                                    # [set][rank] -> device pointer valid in this process
+        with torch.cuda.device(self.device):
+            for s_ in range(2):
+                row = []
+                for r in range(self.world):
+                    if r == self.rank:
+                        row.append(self._own[s_])
+                    else:
+                        ptr = C.c_void_p()
+                        _cabi.check(lib.sage3_shared_open(gathered[r][s_], C.byref(ptr)), "sage3_shared_open")
+                        row.append(ptr.value)
+                self._peer.append(row)
+        self._views = []
+        for s_ in range(2):
+            raw = torch.as_tensor(_DeviceBytes(self._own[s_], self._set_bytes), device=self.device)
+            o = self._offs
+            q_v = raw[o[0]:o[1]].view(dtype).view(B, Hq, self.n, D)
+            k_v = raw[o[1]:o[2]].view(dtype).view(B, Hkv, self.n, D)
+            v_v = raw[o[2]:o[3]].view(dtype).view(B, Hkv, self.n, D)
+            out_v = raw[o[3]:].view(dtype).view(B, Hq, self.n, D)
+            self._views.append((q_v, k_v, v_v, out_v))
+        self._flag = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._calls = 0
+        self._prob = None
+        dist.all_reduce(self._flag, group=group)            # every rank has mapped every buffer before anyone touches one
+        torch.cuda.synchronize(self.device)
+
+    def stage(self):
+        """(q, k, v) views of the buffers the NEXT call reads: [B, Hq, n, D], [B, Hkv, n, D] x 2.  A caller that writes
+        its projections there directly and then passes these very views to the call saves the staging copy."""
+        return self._views[self._calls % 2][:3]
+
+    def _parts(self, set_idx: int, which: int, head0: int, heads_total: int):
+        from . import _cabi
+        p = _cabi.Sage3Parts()
+        p.parts, p.rows_per_part = self.world, self.n
+        off = self._offs[which] + head0 * self.n * self.D * self._es
+        for r in range(self.world):
+            p.base[r] = self._peer[set_idx][r] + off
+        return p
+
+    def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool = False, sm_scale=None,
+                 per_block_mean: bool = True) -> torch.Tensor:
+        import ctypes as C
+        from . import _cabi
+        from .api import Sage3Problem
+        set_idx = self._calls % 2
+        self._calls += 1
+        q_v, k_v, v_v, out_v = self._views[set_idx]
+        for dst, src in ((q_v, q), (k_v, k), (v_v, v)):
+            if src.data_ptr() != dst.data_ptr():
+                dst.copy_(src)
+        dist.all_reduce(self._flag, group=self.group)       # all shards staged (and every rank is done with this set's last use)
+        P, hq_l, hkv_l, N = self.world, self.Hq // self.world, self.Hkv // self.world, self.world * self.n
+        if self._prob is None:
+            # descriptor and workspace of the local problem: hq_l heads over all N tokens, addressed inside every rank's
+            # buffer with that buffer's strides ([B, H, n, D])
+            self._prob = Sage3Problem.for_shape(self.B, hq_l, hkv_l, N, N, self.D, self.dtype, self.device, is_causal=is_causal,
+                                                sm_scale=sm_scale, per_block_mean=per_block_mean,
+                                                q_stride=(self.Hq * self.n * self.D, self.n * self.D, self.D),
+                                                k_stride=(self.Hkv * self.n * self.D, self.n * self.D, self.D),
+                                                o_stride=(self.Hq * self.n * self.D, self.n * self.D, self.D))
+        prob = self._prob
+        prob.desc.is_causal = int(bool(is_causal))
+        lib = _cabi.lib()
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        with torch.cuda.device(self.device):
+            qp = self._parts(set_idx, 0, self.rank * hq_l, self.Hq)
+            kp = self._parts(set_idx, 1, self.rank * hkv_l, self.Hkv)
+            vp = self._parts(set_idx, 2, self.rank * hkv_l, self.Hkv)
+            op = self._parts(set_idx, 3, self.rank * hq_l, self.Hq)
+            _cabi.check(lib.sage3_prepass_parts(C.byref(prob.desc), C.byref(qp), C.byref(kp), C.byref(vp),
+                                                prob.ws.buf.data_ptr(), stream), "sage3_prepass_parts")
+            _cabi.check(lib.sage3_attn_fwd_parts(C.byref(prob.desc), prob.ws.buf.data_ptr(), C.byref(op), None, stream),
+                        "sage3_attn_fwd_parts")
+        dist.all_reduce(self._flag, group=self.group)       # every rank's rows have arrived in every output buffer
+        return out_v
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers and frees this rank's (collective: every rank must call it)."""
+        from . import _cabi
+        if self._peer is None:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        lib = _cabi.lib()
+        with torch.cuda.device(self.device):
+            for s_ in range(2):
+                for r in range(self.world):
+                    if r != self.rank:
+                        lib.sage3_shared_close(self._peer[s_][r])
+            dist.barrier(group=self.group)
+            self._views = None
+            for ptr in self._own:
+                lib.sage3_shared_free(ptr)
+        self._peer = None

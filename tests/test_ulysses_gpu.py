@@ -125,3 +125,48 @@ def test_ring_attention_two_gpus(cuda_device):
             c_one, c_full, c_ref = ret[r]
             print(f"rank {r}: ring vs single GPU cos {c_one:.4f} | ring vs fp32 {c_full:.4f} | single GPU vs fp32 {c_ref:.4f}")
             assert c_one > 0.97 and c_full > c_ref - 0.01
+
+
+def _worker_peer(rank, world, port, ret):
+    import torch.distributed as dist
+    from oracle import sage3_oracle as O
+    from sageattention_b200 import sageattn3
+    from sageattention_b200.ulysses import PeerUlysses
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        B, Hq, Hkv, N, D = 2, 8, 4, 1000, 64                                           # ragged N, GQA
+        n = N // world
+        pu = PeerUlysses(B, Hq, Hkv, n, D, torch.bfloat16, device=dev)
+        ok = True
+        for it in range(3):                                                          # three calls: both buffer sets, and reuse
+            q, k, v = O.make_inputs(B, Hq, Hkv, N, N, D, seed=31 + it, k_outlier_channels=4)
+            cut = lambda x: x[:, :, rank * n:(rank + 1) * n].contiguous().to(dev)
+            if it == 1:                                                              # the caller writes into the staging views
+                sq, sk, sv = pu.stage()
+                sq.copy_(cut(q)); sk.copy_(cut(k)); sv.copy_(cut(v))
+                out = pu(sq, sk, sv)
+            else:
+                out = pu(cut(q), cut(k), cut(v))
+            full = sageattn3(q.to(dev), k.to(dev), v.to(dev))
+            torch.cuda.synchronize()
+            ok = ok and bool(torch.equal(out, full[:, :, rank * n:(rank + 1) * n]))
+        ret[rank] = ok
+        pu.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_ulysses_two_gpus_bit_identical(cuda_device):
+    """Peer-to-peer sequence parallelism (token shards read and written in place over NVLink, no all-to-all): same bits
+    as the single-GPU call, over several calls."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker_peer, args=(world, _free_port(), ret), nprocs=world, join=True)
+        assert dict(ret) == {0: True, 1: True}
