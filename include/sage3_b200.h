@@ -133,6 +133,35 @@ SAGE3_API int sage3_prepass_kmean(const Sage3Desc* desc, const void* q, const vo
                                   void* stream);
 
 /*
+ * Attention over one key range of a longer attention, with the accumulator state carried from call to call.
+ * One attention over keys [0, Nk_total) may be computed as several calls over consecutive key ranges, walked from the
+ * LAST range to the FIRST (the order in which the kernel walks the key blocks of a single call, mainloop_tma_ws.h:509,
+ * 865): every call but the first passes the state the previous one left (o_in / m_in / l_in), every call but the last
+ * asks for it (o_out / m_out / l_out; `out` may then be NULL), the last call writes `out` (and `lse`).  When every
+ * range but the last is a multiple of 128 keys and the pre-pass of every range used the K mean of the whole sequence
+ * (sage3_prepass_kmean), the result equals the single call's bit for bit: the same blocks in the same order with the
+ * same arithmetic.  This is the building block of context-parallel ("ring") attention and of key/value streaming; the
+ * reference offers `return_lse` for that use (sageattention/core.py:120-122), which cannot reproduce the single call
+ * because the FP4 rounding of P depends on the running maximum when a block is processed.
+ *   o: fp32 [B][Hq][Nq][D] unnormalized accumulator; m: fp32 [B][Hq][Nq] running maximum of the smoothed scores; l: fp32
+ *   [B][Hq][Nq][2] the two partial row sums the kernel keeps per row (keys 0-63 and 64-127 of every block; carried
+ *   separately so that the additions stay in the single call's order).  In-place (o_in == o_out ...) is allowed.  With is_causal, `causal_shift` (when use_causal_shift != 0)
+ *   replaces Nk - Nq in the mask  key j visible to query i  <=>  j <= i + causal_shift,  j counted inside this call's
+ *   key range: pass  Nk_total - Nq - first_key_of_the_range.
+ */
+typedef struct Sage3Carry {
+    const float* o_in;
+    const float* m_in;
+    const float* l_in;
+    float* o_out;
+    float* m_out;
+    float* l_out;
+    int32_t use_causal_shift;
+    int32_t causal_shift;
+} Sage3Carry;
+SAGE3_API int sage3_attn_fwd_carry(const Sage3Desc* desc, void* ws, const Sage3Carry* carry, void* out, float* lse, void* stream);
+
+/*
  * A tensor whose token dimension is split into `parts` equal pieces that live in different buffers: piece p holds tokens
  * [p * rows_per_part, (p + 1) * rows_per_part) and is addressed with the (b, h, n) strides of Sage3Desc, n counted from
  * the start of the piece.  The buffers may be memory of other GPUs of the node mapped into this process (see

@@ -39,6 +39,11 @@ class Sage3Parts(C.Structure):
     _fields_ = [("parts", C.c_int32), ("rows_per_part", C.c_int32), ("base", C.c_void_p * MAX_PARTS)]
 
 
+class Sage3Carry(C.Structure):
+    _fields_ = [("o_in", C.c_void_p), ("m_in", C.c_void_p), ("l_in", C.c_void_p), ("o_out", C.c_void_p), ("m_out", C.c_void_p),
+                ("l_out", C.c_void_p), ("use_causal_shift", C.c_int32), ("causal_shift", C.c_int32)]
+
+
 class Sage3Error(RuntimeError):
     def __init__(self, code: int, where: str):
         self.code = code
@@ -81,6 +86,8 @@ def lib() -> C.CDLL:
     l.sage3_prepass_parts.argtypes = [P(Sage3Desc), P(Sage3Parts), P(Sage3Parts), P(Sage3Parts), V, V]
     l.sage3_attn_fwd_parts.restype = C.c_int
     l.sage3_attn_fwd_parts.argtypes = [P(Sage3Desc), V, P(Sage3Parts), V, V]
+    l.sage3_attn_fwd_carry.restype = C.c_int
+    l.sage3_attn_fwd_carry.argtypes = [P(Sage3Desc), V, P(Sage3Carry), V, V, V]
     l.sage3_shared_alloc.restype = C.c_int
     l.sage3_shared_alloc.argtypes = [C.c_size_t, P(C.c_void_p), C.c_char_p]
     l.sage3_shared_open.restype = C.c_int
@@ -107,7 +114,7 @@ def lib() -> C.CDLL:
 
 EXPORTED = ["sage3_version", "sage3_strerror", "sage3_workspace_layout", "sage3_workspace_bytes", "sage3_prepass",
             "sage3_attn_fwd", "sage3_fwd", "sage3_check_status", "sage3_kmean_noalloc", "sage3_selftest_wait_timeout", "sage3_slab_copy", "sage3_merge_partial",
-            "sage3_prepass_kmean", "sage3_prepass_parts", "sage3_attn_fwd_parts", "sage3_shared_alloc", "sage3_shared_open",
+            "sage3_prepass_kmean", "sage3_prepass_parts", "sage3_attn_fwd_parts", "sage3_attn_fwd_carry", "sage3_shared_alloc", "sage3_shared_open",
             "sage3_shared_close", "sage3_shared_free"]
 
 

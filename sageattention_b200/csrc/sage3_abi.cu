@@ -102,13 +102,22 @@ sage3::PartsPtr one_part(const void* p) {
     return r;
 }
 
-int attn_impl(const Sage3Desc* desc, void* ws, const sage3::PartsPtr& out, float* lse, float* debug, void* stream) {
+int attn_impl(const Sage3Desc* desc, void* ws, const sage3::PartsPtr& out, float* lse, float* debug, void* stream,
+              const Sage3Carry* carry = nullptr) {
     Sage3Workspace w;
     int rc = layout(desc, &w);
     if (rc != SAGE3_OK) return rc;
-    if (!ws || !out.base[0]) return SAGE3_E_NULL;
+    if (!ws) return SAGE3_E_NULL;
+    if (!out.base[0] && !(carry && carry->o_out)) return SAGE3_E_NULL;      // somewhere the result must go
     if (lse != nullptr && !aligned(lse, 4)) return SAGE3_E_ALIGN;
     if (!aligned(ws, kWsAlign) || !aligned(out.base[0], 16)) return SAGE3_E_ALIGN;
+    if (carry) {
+        if ((carry->o_in != nullptr) != (carry->m_in != nullptr) || (carry->o_in != nullptr) != (carry->l_in != nullptr)) return SAGE3_E_NULL;
+        if ((carry->o_out != nullptr) != (carry->m_out != nullptr) || (carry->o_out != nullptr) != (carry->l_out != nullptr)) return SAGE3_E_NULL;
+        if (!aligned(carry->o_in, 16) || !aligned(carry->o_out, 16) || !aligned(carry->m_in, 4) || !aligned(carry->l_in, 4) ||
+            !aligned(carry->m_out, 4) || !aligned(carry->l_out, 4))
+            return SAGE3_E_ALIGN;
+    }
     rc = check_arch();
     if (rc != SAGE3_OK) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -131,6 +140,9 @@ int attn_impl(const Sage3Desc* desc, void* ws, const sage3::PartsPtr& out, float
     a.lse = lse;
     a.qkm = reinterpret_cast<const float*>(base + w.qkm);
     for (int i = 0; i < 3; ++i) a.os[i] = desc->o_stride[i];
+    a.carry_o_in = carry ? carry->o_in : nullptr; a.carry_m_in = carry ? carry->m_in : nullptr; a.carry_l_in = carry ? carry->l_in : nullptr;
+    a.carry_o_out = carry ? carry->o_out : nullptr; a.carry_m_out = carry ? carry->m_out : nullptr; a.carry_l_out = carry ? carry->l_out : nullptr;
+    a.causal_shift = (carry && carry->use_causal_shift) ? carry->causal_shift : desc->Nk - desc->Nq;
     a.status = reinterpret_cast<int*>(base + w.status) + kAttnStatusWord;
     a.prepass_status = reinterpret_cast<const int*>(base + w.status);
 #ifdef SAGE3_DEV_TRACE
@@ -316,6 +328,11 @@ SAGE3_API int sage3_prepass_parts(const Sage3Desc* desc, const Sage3Parts* q, co
     if (rc == SAGE3_OK) rc = to_parts(v, desc->Nk, &vp);
     if (rc != SAGE3_OK) return rc;
     return prepass_impl(desc, qp, kp, vp, nullptr, ws, stream);
+}
+
+SAGE3_API int sage3_attn_fwd_carry(const Sage3Desc* desc, void* ws, const Sage3Carry* carry, void* out, float* lse, void* stream) {
+    if (!carry) return SAGE3_E_NULL;
+    return attn_impl(desc, ws, one_part(out), lse, nullptr, stream, carry);
 }
 
 SAGE3_API int sage3_attn_fwd_parts(const Sage3Desc* desc, void* ws, const Sage3Parts* out, float* lse, void* stream) {

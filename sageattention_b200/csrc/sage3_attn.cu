@@ -78,6 +78,10 @@ struct AttnParams {
     float sm_scale;
     int* status;
     const int* prepass_status;
+    // accumulator state carried between calls that walk consecutive key ranges of one attention (nullptr: none)
+    const float *carry_o_in, *carry_m_in, *carry_l_in;   // fp32 [B*Hq][Nq][D] unnormalized O; [B*Hq][Nq] running max; [B*Hq][Nq][2] partial row sums
+    float *carry_o_out, *carry_m_out, *carry_l_out;
+    int causal_shift;                   // key j is visible to query i iff j <= i + causal_shift
 #ifdef SAGE3_DEV_TRACE
     float* debug;                       // development dump of CTA 0 (nullptr in normal use)
 #endif
@@ -176,7 +180,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int nv = (mt0 + 1 < p.nqt) ? 2 : 1;            // query tiles this CTA really has
     const int b = bhq / p.Hq, hq = bhq % p.Hq;
     const int bhkv = b * p.Hkv + hq / (p.Hq / p.Hkv);
-    const int shift = p.Nk - p.Nq;
+    const int shift = p.causal_shift;
     // an earlier CTA of this launch gave up, or the pre-pass did (the workspace is then incomplete)
     const bool dead_launch = (*reinterpret_cast<volatile int*>(p.status) != 0) || (*reinterpret_cast<const volatile int*>(p.prepass_status) != 0);
     // KV blocks of tile t: [0, nbt[t]); the CTA walks block n = nbmax - 1 ... 0 and tile t joins at step skip[t]
@@ -352,7 +356,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
                     for (int ks = 0; ks < 2; ++ks)
                         tc_mma_nvfp4(tmem + C::cO + t * 128, p_desc + 2 * ks, v_desc + 2 * ks, idesc_pv, tmem + C::cSfP + 4 * ks,
-                                     tmem + C::cSfV + 4 * ks, (j > 0) || (ks > 0));
+                                     tmem + C::cSfV + 4 * ks, (j > 0) || (ks > 0) || (p.carry_o_in != nullptr));
                     tc_commit(bar(bPV + pb));
                     TR(17, jj, 4 * t + 1)
                 }
@@ -388,6 +392,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         int xphase = 0;
         float m_run = -INFINITY, l_run = 0.f;
         bool alive = true;
+        const bool carry_in = (p.carry_o_in != nullptr);
+        const size_t crow = (size_t)bhq * p.Nq + grow;           // row of the carried state
+        if (carry_in && t < nv && !dead_launch) {
+            // resume: the accumulator continues from the state an earlier call left (its key range came later in the walk)
+            const bool live = grow < p.Nq;
+            m_run = live ? p.carry_m_in[crow] : -INFINITY;
+            l_run = live ? p.carry_l_in[2 * crow + h] : 0.f;          // each of the row's two threads keeps its own partial sum
+            if (nb > 0) {
+#pragma unroll
+                for (int cc = 0; cc < D / 64; ++cc) {
+                    float o[32];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float4 v4 = live ? *reinterpret_cast<const float4*>(p.carry_o_in + crow * D + (D / 2) * h + cc * 32 + 4 * i)
+                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+                        o[4 * i] = v4.x; o[4 * i + 1] = v4.y; o[4 * i + 2] = v4.z; o[4 * i + 3] = v4.w;
+                    }
+                    tmem_st32(o_addr + cc * 32, o);
+                }
+                tc_wait_st();
+            }
+        }
         PT_DECL
         for (int j = 0; j < nb; ++j) {
             const int n = nb - 1 - j, pb = t * 2 + (j & 1);
@@ -496,8 +522,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             PT(5)
             // This thread's half of the O row times alpha before the block's P V is added (only when a row of the
             // warp moved its maximum); the P V MMA of block j - 1 must have landed first
-            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
-                if (!warp_wait(bar(bPV + (pb ^ 1)), ((j - 1) >> 1) & 1, abort_flag, p.status, kWaitOReady)) { alive = false; break; }
+            if ((j > 0 || carry_in) && __any_sync(0xffffffffu, alpha != 1.0f)) {
+                if (j > 0 && !warp_wait(bar(bPV + (pb ^ 1)), ((j - 1) >> 1) & 1, abort_flag, p.status, kWaitOReady)) { alive = false; break; }
                 tc_fence_after();
                 const uint64_t a2 = pack2f(alpha, alpha);
 #pragma unroll
@@ -544,17 +570,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
             if (alive) {
                 const float inv_l = (l_tot == 0.f || l_tot != l_tot) ? 0.f : __frcp_rn(l_tot);
+                const bool want_out = (p.out[0] != nullptr);
                 // the row's home: one output buffer, or the part that owns this token (another GPU's memory when the
                 // output goes straight back to the token shards of a sequence-parallel group: plain stores)
                 const int opart = (p.out_rows == 0) ? 0 : min(grow / p.out_rows, kMaxParts - 1);
                 const int orow_l = grow - opart * p.out_rows;
                 OutT* orow = static_cast<OutT*>(p.out[opart]) + b * p.os0 + hq * p.os1 + (int64_t)orow_l * p.os2 + (D / 2) * h;
+                if (p.carry_o_out != nullptr && grow < p.Nq) {
+                    if (h == 0) p.carry_m_out[crow] = m_run;
+                    p.carry_l_out[2 * crow + h] = l_run;
+                }
 #pragma unroll
                 for (int cc = 0; cc < D / 64; ++cc) {
                     float o[32];
                     if (nb > 0) {
                         tmem_ld32(o_addr + cc * 32, o);
                         tc_wait_ld();
+                    } else if (carry_in && grow < p.Nq) {
+                        // no key block of this call is visible to the tile: the state passes through
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float4 v4 = *reinterpret_cast<const float4*>(p.carry_o_in + crow * D + (D / 2) * h + cc * 32 + 4 * i);
+                            o[4 * i] = v4.x; o[4 * i + 1] = v4.y; o[4 * i + 2] = v4.z; o[4 * i + 3] = v4.w;
+                        }
                     } else {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) o[i] = 0.f;
@@ -563,7 +601,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                         for (int i = 0; i < 32; ++i) p.debug[16384 + 512 + r * D + (D / 2) * h + cc * 32 + i] = o[i];
                         if (cc == 0 && h == 0) p.debug[16384 + 384 + r] = l_tot;
                     })
-                    if (grow < p.Nq) {
+                    if (p.carry_o_out != nullptr && grow < p.Nq) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            *reinterpret_cast<float4*>(p.carry_o_out + crow * D + (D / 2) * h + cc * 32 + 4 * i) =
+                                make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                    }
+                    if (want_out && grow < p.Nq) {
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             uint4 w;
@@ -664,6 +708,9 @@ cudaError_t launch_attn(const AttnArgs& a, cudaStream_t st, int* driver_rc) {
     p.os0 = a.os[0]; p.os1 = a.os[1]; p.os2 = a.os[2];
     p.status = a.status;
     p.prepass_status = a.prepass_status;
+    p.carry_o_in = a.carry_o_in; p.carry_m_in = a.carry_m_in; p.carry_l_in = a.carry_l_in;
+    p.carry_o_out = a.carry_o_out; p.carry_m_out = a.carry_m_out; p.carry_l_out = a.carry_l_out;
+    p.causal_shift = a.causal_shift;
 #ifdef SAGE3_DEV_TRACE
     p.debug = a.debug;
 #endif

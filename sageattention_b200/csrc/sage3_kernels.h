@@ -43,6 +43,10 @@ struct AttnArgs {
     float* lse;                     // optional fp32 [B][Hq][Nq]; nullptr if not wanted
     const float* qkm;               // fp32 [B][Hq][Nq_p] from the pre-pass
     int* status;                    // the attention kernel's status word
+    // accumulator state carried between calls (all nullptr: none); fp32, unnormalized O [B][Hq][Nq][D], m [B][Hq][Nq], l [B][Hq][Nq][2]
+    const float *carry_o_in, *carry_m_in, *carry_l_in;
+    float *carry_o_out, *carry_m_out, *carry_l_out;
+    int causal_shift;               // key j visible to query i iff j <= i + causal_shift (Nk - Nq unless the caller offsets it)
     const int* prepass_status;      // the pre-pass's status word (non-zero: the workspace is incomplete, do nothing)
 #ifdef SAGE3_DEV_TRACE
     float* debug;                   // development dump of the first CTA; nullptr in normal use

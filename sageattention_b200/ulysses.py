@@ -10,10 +10,12 @@ Two schemes, as the reference's parallel example uses them through xfuser
   quantization need the whole sequence of a head, so they run after the exchange), a second all-to-all
   returns the output to token shards (`ulysses_attention`).
 
-For head counts smaller than (or not divisible by) the number of GPUs there is ring attention on the same token
-shards (`ring_attention`): K / V shards travel around the ring while every rank attends its queries to the shard it
-holds, and the partial results are merged through their log-sum-exp (the use `return_lse` exists for,
-sageattention/core.py:120-122).
+For head counts smaller than (or not divisible by) the number of GPUs there is context parallelism on the same token
+shards: `context_parallel_attention` walks the key shards in the single call's block order with the accumulator state
+carried from shard to shard, which reproduces the single-GPU result exactly (causal masks included);
+`ring_attention` is the classical form (K / V shards travel around the ring, partial results merged through their
+log-sum-exp, the use `return_lse` exists for, sageattention/core.py:120-122), which for FP4 attention is a slightly
+different function.
 
 With `ulysses_attention` and `ring_attention` the exchanged tensors land in this GPU's own memory (NCCL) before any
 kernel reads them.  `PeerUlysses` is the peer-to-peer form of the same exchange on one NVSwitch node: the token shards
@@ -261,6 +263,92 @@ def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_lay
         if kv_next is not None:
             kv = kv_next
     return out if tensor_layout == "HND" else out.transpose(1, 2)
+
+
+def context_parallel_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
+                               is_causal: bool = False, sm_scale=None, per_block_mean: bool = True,
+                               group: dist.ProcessGroup | None = None, return_lse: bool = False):
+    """Context-parallel attention that equals the single-GPU call: every rank passes its contiguous token shard of all
+    heads (q [B,Hq,n,D], k, v [B,Hkv,n,D] for "HND"; rank r owns tokens [r n, (r + 1) n)) and gets the output for its
+    queries.  No head-count condition; causal masks supported.
+
+    How it differs from `ring_attention`: the key shards are walked in the order in which a single call walks its key
+    blocks -- from the LAST shard to the FIRST -- with the accumulator state (unnormalized O, running maximum, row sum)
+    carried from shard to shard (`sage3_attn_fwd_carry`), and every shard is smoothed with the K mean of the whole
+    sequence (`sage3_prepass_kmean`; the mean is formed from the ranks' partial column sums in the single call's
+    summation order).  The blocks, their order and the arithmetic are then the single call's: for shard lengths
+    that are multiples of 512 tokens the result is bit-identical to `sageattn3` on the gathered tensors (multiples of
+    128: identical up to the last bit of the K mean).  Each step's shard is broadcast by its owner (NCCL) while the
+    previous shard is being attended; under a causal mask a rank skips the shards that lie entirely in its future.
+    """
+    import ctypes as C
+    from . import _cabi
+    from .api import Sage3Problem
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    qh, kh, vh = (_to_hnd(t, tensor_layout).contiguous() for t in (q, k, v))
+    B, Hq, n, D = qh.shape
+    Hkv, dev, dt = kh.shape[1], qh.device, qh.dtype
+    if kh.shape[2] != n:
+        raise ValueError("context_parallel_attention shards queries and keys alike (self-attention)")
+    lib = _cabi.lib()
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    out = torch.empty_like(qh)
+    lse = torch.empty(B, Hq, n, dtype=torch.float32, device=dev) if return_lse else None
+    prob = Sage3Problem(qh, kh, vh, "HND", is_causal, sm_scale, per_block_mean, out=out)
+
+    # K mean of the whole sequence, in the single call's order: per-rank partial column sums (512-row chunks, written by
+    # the pre-pass into its workspace), gathered, added chunk by chunk in fp32, scaled by 1 / N, rounded once
+    prob.prepass()
+    lay = prob.ws.layout
+    chunks = lay.kchunks
+    kpart = prob.ws.buf[lay.kpart: lay.kpart + B * Hkv * chunks * D * 4].view(torch.float32).view(B * Hkv, chunks, D)
+    allpart = torch.empty(world, B * Hkv, chunks, D, dtype=torch.float32, device=dev)
+    dist.all_gather_into_tensor(allpart, kpart.contiguous(), group=group)
+    acc = torch.zeros(B * Hkv, D, dtype=torch.float32, device=dev)
+    for r_ in range(world):
+        for c_ in range(chunks):
+            acc = acc + allpart[r_, :, c_]
+    inv = torch.tensor(1.0, dtype=torch.float32, device=dev) / torch.tensor(float(world * n), dtype=torch.float32, device=dev)
+    km = (acc * inv).to(dt).contiguous()
+
+    o_acc = torch.empty(B, Hq, n, D, dtype=torch.float32, device=dev)
+    m_acc = torch.empty(B, Hq, n, dtype=torch.float32, device=dev)
+    l_acc = torch.empty(B, Hq, n, 2, dtype=torch.float32, device=dev)
+    mine = torch.stack((kh, vh))
+    order = list(range(world - 1, -1, -1))                     # last shard first
+    grank = (lambda r_: dist.get_global_rank(group, r_)) if group is not None else (lambda r_: r_)
+
+    def fetch(s_):
+        buf = mine if s_ == rank else torch.empty_like(mine)
+        return buf, dist.broadcast(buf, src=grank(s_), group=group, async_op=True)
+
+    nxt = fetch(order[0])
+    started = False
+    for i, s_ in enumerate(order):
+        buf, work = nxt
+        if i + 1 < world:
+            nxt = fetch(order[i + 1])                          # travels while this shard is attended
+        work.wait()
+        if is_causal and s_ > rank:
+            continue                                           # entirely in the future of this rank's queries
+        last = (s_ == 0)
+        c = _cabi.Sage3Carry()
+        if started:
+            c.o_in, c.m_in, c.l_in = o_acc.data_ptr(), m_acc.data_ptr(), l_acc.data_ptr()
+        if not last:
+            c.o_out, c.m_out, c.l_out = o_acc.data_ptr(), m_acc.data_ptr(), l_acc.data_ptr()
+        if is_causal:
+            c.use_causal_shift, c.causal_shift = 1, (rank - s_) * n
+        with torch.cuda.device(dev):
+            _cabi.check(lib.sage3_prepass_kmean(C.byref(prob.desc), qh.data_ptr(), buf[0].data_ptr(), buf[1].data_ptr(),
+                                                km.data_ptr(), prob.ws.buf.data_ptr(), stream), "sage3_prepass_kmean")
+            _cabi.check(lib.sage3_attn_fwd_carry(C.byref(prob.desc), prob.ws.buf.data_ptr(), C.byref(c),
+                                                 out.data_ptr() if last else None,
+                                                 lse.data_ptr() if (last and lse is not None) else None, stream),
+                        "sage3_attn_fwd_carry")
+        started = True
+    o = out if tensor_layout == "HND" else out.transpose(1, 2)
+    return (o, lse) if return_lse else o
 
 
 # ------------------------------------------------------------------------------------------------------

@@ -76,3 +76,53 @@ def test_prepass_with_supplied_k_mean(cuda_device):
     assert torch.equal(s["k_codes"], w["k_codes"][:, :, half]) and torch.equal(s["k_sf"], w["k_sf"][:, :, half])
     assert torch.equal(s["delta"], w["delta"][..., half])
     assert torch.equal(s["vt_codes"], w["vt_codes"][..., half])
+
+
+def _carry(o_in=None, m_in=None, l_in=None, o_out=None, m_out=None, l_out=None, shift=None):
+    c = _cabi.Sage3Carry()
+    for name, t in (("o_in", o_in), ("m_in", m_in), ("l_in", l_in), ("o_out", o_out), ("m_out", m_out), ("l_out", l_out)):
+        setattr(c, name, None if t is None else t.data_ptr())
+    if shift is not None:
+        c.use_causal_shift, c.causal_shift = 1, shift
+    return c
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Nq,cuts,D,causal", [
+    (1, 2, 2, 384, [0, 256, 640, 1000], 128, False),       # three key ranges, the last one ragged
+    (2, 4, 2, 300, [0, 128, 300], 64, True),               # causal, GQA, Nq == Nk
+    (1, 2, 1, 200, [0, 384, 768], 128, True),              # causal, Nk > Nq (bottom-right aligned)
+])
+def test_key_ranges_with_carried_state_equal_one_call(cuda_device, B, Hq, Hkv, Nq, cuts, D, causal):
+    """One attention computed as several calls over consecutive key ranges, walked from the last range to the first
+    with the accumulator state carried along: the same bits as the single call (same blocks, same order)."""
+    from tests._util import read_workspace
+    Nk = cuts[-1]
+    q, k, v = (t.to(cuda_device) for t in O.make_inputs(B, Hq, Hkv, Nq, Nk, D, seed=90 + Nq, k_offset_std=1.5))
+    whole = Sage3Problem(q, k, v, is_causal=causal, return_lse=True)
+    ref = whole.run().clone()
+    ref_lse = whole.lse.clone()
+    torch.cuda.synchronize()
+    km = read_workspace(whole)["km"].to(cuda_device)
+
+    lib, st = _cabi.lib(), torch.cuda.current_stream(cuda_device).cuda_stream
+    o_acc = torch.empty(B, Hq, Nq, D, dtype=torch.float32, device=cuda_device)
+    m_acc = torch.empty(B, Hq, Nq, dtype=torch.float32, device=cuda_device)
+    l_acc = torch.empty(B, Hq, Nq, 2, dtype=torch.float32, device=cuda_device)
+    out = torch.full_like(q, float("nan"))
+    lse = torch.empty(B, Hq, Nq, dtype=torch.float32, device=cuda_device)
+    ranges = list(zip(cuts[:-1], cuts[1:]))[::-1]                      # last range first
+    for idx, (k0, k1) in enumerate(ranges):
+        ks, vs = k[:, :, k0:k1].contiguous(), v[:, :, k0:k1].contiguous()
+        prob = Sage3Problem(q, ks, vs, is_causal=causal, out=out)
+        assert lib.sage3_prepass_kmean(C.byref(prob.desc), q.data_ptr(), ks.data_ptr(), vs.data_ptr(), km.data_ptr(),
+                                       prob.ws.buf.data_ptr(), st) == 0
+        first, last = idx == 0, idx == len(ranges) - 1
+        carry = _carry(*((None, None, None) if first else (o_acc, m_acc, l_acc)),
+                       *((None, None, None) if last else (o_acc, m_acc, l_acc)),
+                       shift=(Nk - Nq - k0) if causal else None)
+        rc = lib.sage3_attn_fwd_carry(C.byref(prob.desc), prob.ws.buf.data_ptr(), C.byref(carry),
+                                      out.data_ptr() if last else None, lse.data_ptr() if last else None, st)
+        assert rc == 0
+        assert prob.check_status() == 0
+    assert torch.equal(out, ref)
+    assert torch.equal(lse, ref_lse)

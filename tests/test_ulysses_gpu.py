@@ -170,3 +170,40 @@ def test_peer_ulysses_two_gpus_bit_identical(cuda_device):
         ret = mgr.dict()
         mp.spawn(_worker_peer, args=(world, _free_port(), ret), nprocs=world, join=True)
         assert dict(ret) == {0: True, 1: True}
+
+
+def _worker_cp(rank, world, port, ret):
+    import torch.distributed as dist
+    from oracle import sage3_oracle as O
+    from sageattention_b200 import sageattn3
+    from sageattention_b200.ulysses import context_parallel_attention
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        res = []
+        for causal, (Hq, Hkv, n, D) in ((False, (3, 3, 1024, 128)), (True, (4, 2, 512, 64)), (True, (3, 1, 1024, 128))):
+            N = n * world
+            q, k, v = O.make_inputs(1, Hq, Hkv, N, N, D, seed=35 + n + Hq, k_offset_std=1.0)
+            cut = lambda x: x[:, :, rank * n:(rank + 1) * n].contiguous().to(dev)
+            out, lse = context_parallel_attention(cut(q), cut(k), cut(v), is_causal=causal, return_lse=True)
+            one, lse1 = sageattn3(q.to(dev), k.to(dev), v.to(dev), is_causal=causal, return_lse=True)
+            torch.cuda.synchronize()
+            res.append(bool(torch.equal(out, one[:, :, rank * n:(rank + 1) * n])) and
+                       bool(torch.equal(lse, lse1[:, :, rank * n:(rank + 1) * n])))
+        ret[rank] = res
+    finally:
+        dist.destroy_process_group()
+
+
+def test_context_parallel_two_gpus_bit_identical(cuda_device):
+    """Key shards walked in the single call's order with the accumulator state carried along, K smoothed with the mean of
+    the whole sequence: the same bits as sageattn3 on the gathered tensors, causal masks and odd head counts included."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker_cp, args=(2, _free_port(), ret), nprocs=2, join=True)
+        assert dict(ret) == {0: [True, True, True], 1: [True, True, True]}
