@@ -50,8 +50,10 @@ enum { SAGE3_FP16 = 0, SAGE3_BF16 = 1 };
  * Problem description.  Tensors are addressed as x[b][h][n][d] with the element strides given here and
  * d contiguous, so "HND" ([B,H,N,D]) and "NHD" ([B,N,H,D]) callers use the same code path
  * (the keyword surface of sageattention/core.py:79-157 `tensor_layout`).
- * GQA: query head h reads kv head h / (Hq / Hkv).  Causal masks are bottom-right aligned
- * (key j is visible to query i iff j <= i + Nk - Nq), as in blackwell/mainloop_tma_ws.h:286-289.
+ * GQA: query head h reads kv head h / (Hq / Hkv).  Causal masks are bottom-right aligned on the REAL lengths
+ * (key j is visible to query i iff j <= i + Nk - Nq; the flash-attention convention).  The reference aligns on the
+ * lengths padded to 128 (blackwell/mainloop_tma_ws.h:286-289 works on the padded sizes): identical when Nq and Nk are
+ * multiples of 128, deliberately different otherwise (e.g. Nq = 300, Nk = 500: a shift of 200 here, 128 there).
  */
 typedef struct Sage3Desc {
     int32_t B, Hq, Hkv, Nq, Nk, D;

@@ -26,7 +26,8 @@ Reference locations (paths inside the reference project):
   .../blackwell/api.cu:142, api.py:127                 softmax scale (D**-0.5 * log2 e)
 
 Deliberate differences from the reference source (documented, not accidental):
-  * masks are applied on the real token index (the reference masks the permuted MMA column index);
+  * masks are applied on the real token index (the reference masks the permuted MMA column index), and the causal
+    mask is aligned on the real lengths (the reference: on the lengths padded to 128);
   * every accumulator starts from zero / -inf;
   * inputs are never modified in place;
   * divisions are IEEE fp32 (the reference compiles with --use_fast_math).
@@ -282,7 +283,8 @@ def attention_from_prepass(pp: Prepass, is_causal: bool = False, sm_scale=None,
     m = torch.full((B, Hq, R, 1), -math.inf)
     l = torch.zeros(B, Hq, R, 1)
     O = torch.zeros(B, Hq, R, D)
-    # causal mask is bottom-right aligned (mainloop_tma_ws.h:286-289, 732-734): key j visible to
+    # causal mask, bottom-right aligned on the real lengths (the reference, mainloop_tma_ws.h:286-289, 732-734,
+    # aligns on the lengths padded to 128: the same whenever Nq and Nk are multiples of 128): key j visible to
     # query i iff j <= i + Nk - Nq
     lim = rows.view(1, 1, R, 1) + (pp.nk - pp.nq)
 

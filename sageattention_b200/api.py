@@ -12,7 +12,9 @@ processor exactly like the reference's.  Differences, all deliberate:
   * no fallback: an unsupported head dim, device or a missing library raises (the reference falls back to
     torch SDPA for D >= 256, api.py:132-134, and the v2 dispatcher raises on sm_100, core.py:156-157);
   * attn_mask other than None raises (the reference ignores it silently);
-  * GQA (Hq a multiple of Hkv), Nq != Nk, "NHD" layout and a per-head sm_scale tensor are accepted.
+  * GQA (Hq a multiple of Hkv), Nq != Nk, "NHD" layout and a per-head sm_scale tensor are accepted;
+  * the causal mask is bottom-right aligned on the real lengths (key j visible to query i iff j <= i + Nk - Nq); the
+    reference aligns on the lengths padded to 128, which is the same whenever both are multiples of 128.
 PyTorch is used for device memory and the current stream only.
 """
 from __future__ import annotations
