@@ -11,9 +11,10 @@
 //                (same lane quarter, different warpgroups): thread h owns keys [64 h, 64 h + 64) of every KV
 //                block and columns [D/2 h, D/2 (h + 1)) of the O row.
 // Per KV block a softmax thread pulls its 64 scores out of tensor memory into registers (the S buffer goes to
-// the other tile as soon as all eight warps have done so), finds its four microblock maxima and runs the exp2
-// pass at once: with E = P~ / sf = 6 * 2^((S - bm) s), the exp2 values and FP4 codes of a microblock depend
-// on the maximum bm of that microblock only.  The running row maximum enters just the E4M3 scales, the row
+// the other tile as soon as all eight warps have done so) and runs the exp2 pass at once, microblock by microblock,
+// the maxima of the next microblock found under the exponentials of the current one: with
+// E = P~ / sf = 6 * 2^((S - bm) s), the exp2 values and FP4 codes of a microblock depend on the maximum bm of that
+// microblock only.  The running row maximum enters just the E4M3 scales, the row
 // sum and the O rescale factor; the two threads of a row exchange their half maxima through shared memory
 // (published before the pass, read after it), so the exchange costs no wait.  Then the thread stores its half
 // of the P row (codes + scales), multiplies its half of the O row by the rescale factor when a row of the
@@ -135,21 +136,6 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) 
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
     const bool ok = mbar_wait(bar, parity, abort_flag, status, code);
     return __all_sync(0xffffffffu, ok);
-}
-
-// Maxima of two 16-key microblocks held in t[0..31] (3-input max: 8 operations per 16 values, depth 3).
-__device__ __forceinline__ void microblock_max2(const float* t, float& m0, float& m1) {
-#pragma unroll
-    for (int g = 0; g < 2; ++g) {
-        const float* x = t + 16 * g;
-        float a = fmax3(x[0], x[1], x[2]);
-        float b = fmax3(x[3], x[4], x[5]);
-        const float c = fmax3(x[6], x[7], x[8]);
-        const float d = fmax3(x[9], x[10], x[11]);
-        a = fmax3(a, x[12], x[13]);
-        b = fmax3(b, x[14], x[15]);
-        (g ? m1 : m0) = fmax3(a, b, fmaxf(c, d));
-    }
 }
 
 template <int D, bool CAUSAL, typename OutT>
@@ -443,19 +429,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             DEV_DUMP(if (dbg && j == 0) {
                 for (int i = 0; i < 64; ++i) p.debug[r * 128 + 64 * h + i] = s[i];
             })
-            // microblock maxima of this half; the half maximum goes to the partner thread
+            // Microblock maxima interleaved with the exp2 pass: E = P~ / sf = 6 * 2^((S - bm) s) of a microblock needs only that
+            // microblock's maximum, so the maxima of microblock g + 1 are found while the exponentials of microblock g are
+            // in flight; the half maximum goes to the partner thread as soon as the last microblock maximum is known (the
+            // partner reads it after its own pass).
             float bm[4];
-            microblock_max2(s, bm[0], bm[1]);
-            microblock_max2(s + 32, bm[2], bm[3]);
-            const float m_half = fmaxf(fmaxf(bm[0], bm[1]), fmaxf(bm[2], bm[3]));
-            xch_mine[(j & 1) * 512] = m_half;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_x);
-            TR(warp - 4, j, 3)
-            PT(2)
-            // exp2 pass: E = P~ / sf = 6 * 2^((S - bm) s) needs the microblock maximum only, not the row maximum
             uint32_t codes[8];
             float se[4];
+            float m_half = -INFINITY;
+            auto mb_max = [&](int g) {
+                const float* x = s + 16 * g;
+                float a = fmax3(x[0], x[1], x[2]);
+                float b = fmax3(x[3], x[4], x[5]);
+                const float c = fmax3(x[6], x[7], x[8]);
+                const float d = fmax3(x[9], x[10], x[11]);
+                a = fmax3(a, x[12], x[13]);
+                b = fmax3(b, x[14], x[15]);
+                bm[g] = fmax3(a, b, fmaxf(c, d));
+            };
+            mb_max(0);
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
                 const float negc = (bm[g] == -INFINITY) ? 0.f : -fmaf(bm[g], sl2, -kLog2Of6);
@@ -467,6 +459,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     unpack2f(fma2(pack2f(s[16 * g + 2 * i], s[16 * g + 2 * i + 1]), sl2x2, negc2), a, b2);
                     e[2 * i] = ex2_approx(a);
                     e[2 * i + 1] = ex2_approx(b2);
+                }
+                if (g < 3) mb_max(g + 1);
+                if (g == 2) {
+                    m_half = fmaxf(fmaxf(bm[0], bm[1]), fmaxf(bm[2], bm[3]));
+                    xch_mine[(j & 1) * 512] = m_half;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_x);
+                    TR(warp - 4, j, 3)
+                    PT(2)
                 }
                 uint64_t acc0 = pack2f(e[0], e[1]), acc1 = pack2f(e[2], e[3]);
                 acc0 = add2(acc0, pack2f(e[4], e[5]));
