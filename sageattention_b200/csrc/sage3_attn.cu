@@ -141,7 +141,7 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 template <int D, bool CAUSAL, typename OutT>
 __global__ void __launch_bounds__(Cfg<D>::kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p) {
     using C = Cfg<D>;
     constexpr int S = C::kStages;
     extern __shared__ uint8_t smem_dyn[];

@@ -98,7 +98,7 @@ __device__ __forceinline__ void quant16(const float* x, uint32_t& lo, uint32_t& 
 // (deterministic: no atomics, the summation order depends on N only)
 // ------------------------------------------------------------------------------------------------
 template <typename T, int D>
-__global__ void __launch_bounds__(256) colsum_partial_kernel(const Src<T> x, int64_t sb, int64_t sh,
+__global__ void __launch_bounds__(256) colsum_partial_kernel(const __grid_constant__ Src<T> x, int64_t sb, int64_t sh,
                                                              int64_t sn, int H, int N,
                                                              float* __restrict__ part, int chunks) {
     constexpr int TPR = D / 8;           // threads per row (8 elements = 16 bytes each)
@@ -148,7 +148,7 @@ enum { kModeQBlockMean = 0, kModeQGlobalMean = 1 };
 
 template <typename T, int D, int MODE>
 __global__ void __launch_bounds__(256, 3) quant_rows_kernel(
-    const Src<T> x, int64_t sb, int64_t sh, int64_t sn, int H, int N, int Np,
+    const __grid_constant__ Src<T> x, int64_t sb, int64_t sh, int64_t sn, int H, int N, int Np,
     const T* __restrict__ mean_in,     // one mean per head: qm [B*H][D]; unused for block mean
     T* __restrict__ qm_out,            // block mean: [B*H][Np/128][D]
     uint8_t* __restrict__ codes,       // [B*H][Np][D/2]
@@ -301,7 +301,7 @@ __global__ void __launch_bounds__(256, 3) quant_rows_kernel(
 // ------------------------------------------------------------------------------------------------
 template <typename T, int D>
 __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
-    const Src<T> x, int64_t sb, int64_t sh, int64_t sn, int H, int N, int Np,
+    const __grid_constant__ Src<T> x, int64_t sb, int64_t sh, int64_t sn, int H, int N, int Np,
     const T* __restrict__ km,          // [B*H][D]
     uint8_t* __restrict__ codes,       // [B*H][Np][D/2]
     uint8_t* __restrict__ sfs,         // [B*H][Np/128][D/64][512]
@@ -466,7 +466,7 @@ __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
 // V: one tile of 128 tokens x D channels per CTA -> V^T codes (microblocks along tokens) + scale atoms
 // ------------------------------------------------------------------------------------------------
 template <typename T, int D>
-__global__ void __launch_bounds__(256) quant_vt_kernel(const Src<T> x, int64_t sb, int64_t sh, int64_t sn,
+__global__ void __launch_bounds__(256) quant_vt_kernel(const __grid_constant__ Src<T> x, int64_t sb, int64_t sh, int64_t sn,
                                                        int H, int N, int Np, uint8_t* __restrict__ codes,
                                                        uint8_t* __restrict__ sfs) {
     constexpr int PITCH = D + 2;          // elements; word pitch odd -> column reads are conflict-free
