@@ -2,14 +2,19 @@
 // accumulators in tensor memory, exp2 online softmax, P re-quantized to NVFP4 before the PV MMA.
 //
 // One CTA per PAIR of 128-row query tiles of one head; every K / V^T stage in shared memory serves both
-// tiles.  Five warpgroups (setmaxnreg moves registers to the softmax warpgroups):
+// tiles.  Six warpgroups (setmaxnreg moves registers to the softmax warpgroups):
 //   warp 0       TMA producer (one lane): both Q tiles once, then K (+ one delta_s row per tile) / V^T /
 //                scale atoms per KV block
 //   warp 1       Q K^T MMA issuer (one lane) and owner of the tensor-memory allocation
 //   warp 2       P V MMA issuer (one lane); warp 3 idle
 //   warps 4-11   softmax of query tile 0, warps 12-19 softmax of query tile 1.  A row is shared by two threads
 //                (same lane quarter, different warpgroups): thread h owns keys [64 h, 64 h + 64) of every KV
-//                block and columns [D/2 h, D/2 (h + 1)) of the O row.
+//                block and, in the epilogue, columns [D/2 h, D/2 (h + 1)) of the O row.
+//   warps 20-23  O rescale ("correction"), one warp per tensor-memory lane quarter: when a row of the quarter moved
+//                its maximum, the warp multiplies the 32 O rows of its quarter by their factors before the block's
+//                P V MMA is issued.  The softmax warps hand the factors over through shared memory and never touch
+//                O inside the loop, so neither the wait for the previous P V nor the tensor-memory round trip sits
+//                in their instruction stream.
 // Per KV block a softmax thread pulls its 64 scores out of tensor memory into registers (the S buffer goes to
 // the other tile as soon as all eight warps have done so) and runs the exp2 pass at once, microblock by microblock,
 // the maxima of the next microblock found under the exponentials of the current one: with
@@ -17,8 +22,7 @@
 // microblock only.  The running row maximum enters just the E4M3 scales, the row
 // sum and the O rescale factor; the two threads of a row exchange their half maxima through shared memory
 // (published before the pass, read after it), so the exchange costs no wait.  Then the thread stores its half
-// of the P row (codes + scales), multiplies its half of the O row by the rescale factor when a row of the
-// warp moved its maximum, and at the end writes its half of O / l.
+// of the P row (codes + scales) and at the end writes its half of O / l.
 // Tensor memory (512 columns) holds one 128-column S buffer, the two O accumulators and the scale factors; the
 // S buffer alternates between the tiles, which keeps the two tiles half a block apart: one pair of warps per
 // scheduler is in its exp2 pass while the other pair loads, reduces and stores.
@@ -91,7 +95,7 @@ struct AttnParams {
 template <int D>
 struct Cfg {
     static constexpr int kStages = 6;                         // K and V^T stages, each shared by the two query tiles
-    static constexpr int kThreads = 640;                      // 5 warpgroups, see the kernel
+    static constexpr int kThreads = 768;                      // 6 warpgroups, see the kernel
     static constexpr int kQBytes = 128 * D / 2;               // per query tile
     static constexpr int kSfQkBytes = (D / 64) * 512;
     static constexpr int kKBytes = 128 * D / 2;
@@ -113,9 +117,10 @@ struct Cfg {
     static constexpr int oOnes = oDelta + kStages * 2 * kDeltaPitch;   // 128 x 16 tile: column 0 = 1.0, rest 0
     static constexpr int oXch = oOnes + 4096;                 // float [2 parities][tile][half][128]: microblock-half maxima; [tile][half][128] row sums
     static constexpr int oBar = oXch + (8 + 4) * 128 * 4;
-    static constexpr int kNumBars = 1 + 4 * kStages + 2 + 1 + 4 + 4 + 8;
+    static constexpr int kNumBars = 1 + 4 * kStages + 2 + 1 + 4 + 4 + 8 + 16 + 4;
     static constexpr int oMisc = oBar + kNumBars * 8;
-    static constexpr int kSmemBytes = oMisc + 64 + 1024;      // + slack for the manual 1024-byte alignment
+    static constexpr int oAlpha = oMisc + 64;                 // rescale factors, float [2 block parities][2 tiles][128 rows]
+    static constexpr int kSmemBytes = oAlpha + 2048 + 1024;      // + slack for the manual 1024-byte alignment
     // tensor-memory columns: one S buffer, one O accumulator per tile, scale factors
     static constexpr uint32_t cS = 0, cO = 128, cSfQ = 384, cSfK = 400, cSfV = 408, cSfP = 416;
     static constexpr uint64_t kSwzQK = (D == 128) ? kSwz64 : kSwz32;
@@ -153,7 +158,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // barriers
     auto bar = [&](int i) { return sbase + C::oBar + 8u * i; };
     const int bQ = 0, bKF = 1, bKE = bKF + S, bVF = bKE + S, bVE = bVF + S, bSF = bVE + S, bSE = bSF + 2,
-              bPF = bSE + 1, bPV = bPF + 4, bXC = bPV + 4;
+              bPF = bSE + 1, bPV = bPF + 4, bXC = bPV + 4, bAL = bXC + 8, bOS = bAL + 16;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + C::oMisc);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + C::oMisc + 8);
 
@@ -199,7 +204,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             mbar_init(bar(bPF + i), 8);    // [tile][buffer]: P (+ scales) written and O rescaled
             mbar_init(bar(bPV + i), 1);    // [tile][buffer]: the P V MMA that read it is complete
         }
-        for (int i = 0; i < 8; ++i) mbar_init(bar(bXC + i), 2);   // [tile][lane quarter]: both half-row warps have published a value
+        for (int i = 0; i < 8; ++i) mbar_init(bar(bXC + i), 2);
+        // [tile][lane quarter][block parity]: the quarter's rescale factors of a block are in shared memory.  One barrier per
+        // block parity: the softmax warp may publish block j + 1 before the correction warp has looked at block j, and
+        // a single barrier would then be two phases ahead of the waiter.
+        for (int i = 0; i < 16; ++i) mbar_init(bar(bAL + i), 1);
+        for (int i = 0; i < 4; ++i) mbar_init(bar(bOS + i), 4);   // [tile][P buffer]: the four correction warps are done with O   // [tile][lane quarter]: both half-row warps have published a value
         mbar_fence_init();
     }
     {
@@ -230,11 +240,51 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
     const float sl2 = p.sm_scale_per_head ? p.sm_scale_per_head[hq] * 1.4426950408889634f : p.sm_scale_log2;
 
-    // Register budget: 640 threads start with 96 registers each, and that allocation (61 440) is all the CTA can
-    // ever hold: 128 x 32 for warpgroup 0 (three single-lane roles) + 512 x 112 for the softmax warpgroups.
-    // (An increase beyond the launch allocation would wait forever.)
-    if (warp < 4) {
-      reg_dealloc<32>();
+    // Register budget: 768 threads start with 80 registers each, and that allocation (61 440) is all the CTA can
+    // ever hold: 128 x kRoleRegs for warpgroup 0 (three single-lane roles) + 128 x kCorrRegs for the correction
+    // warpgroup + 512 x 104 for the softmax warpgroups.  (An increase beyond the launch allocation would wait forever.)
+    constexpr int kRoleRegs = (D == 64) ? 24 : 32, kCorrRegs = 64 - kRoleRegs;
+    if (warp >= 20) {
+      reg_dealloc<kCorrRegs>();
+      // ------------------------------------------------------------------ O rescale (correction), one warp per lane quarter
+      const int quarter = warp & 3;
+      const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+      const float* alpha_s = reinterpret_cast<const float*>(sgen + C::oAlpha);
+      const bool carry_in = (p.carry_o_in != nullptr);
+      bool ok = true;
+      for (int jj = 0; ok && jj < nbmax; ++jj) {
+          for (int t = 0; t < 2; ++t) {
+              if (jj < skip[t]) continue;
+              const int j = jj - skip[t], pb = t * 2 + (j & 1);
+              if (!warp_wait(bar(bAL + (t * 4 + quarter) * 2 + (j & 1)), (j >> 1) & 1, abort_flag, p.status, kWaitAlpha)) { ok = false; break; }
+              const float alpha = alpha_s[((j & 1) * 2 + t) * 128 + quarter * 32 + lane];
+              // block 0 has nothing to rescale unless the accumulator was carried in
+              if ((j > 0 || carry_in) && __any_sync(0xffffffffu, alpha != 1.0f)) {
+                  // the P V MMA of block j - 1 must have landed first
+                  if (j > 0 && !warp_wait(bar(bPV + (pb ^ 1)), ((j - 1) >> 1) & 1, abort_flag, p.status, kWaitOReady)) { ok = false; break; }
+                  tc_fence_after();
+                  const uint64_t a2 = pack2f(alpha, alpha);
+                  const uint32_t o_addr = tmem + lane_addr + C::cO + t * 128;
+#pragma unroll
+                  for (int cc = 0; cc < D / 16; ++cc) {
+                      float o0[16];
+                      tmem_ld16(o_addr + cc * 16, o0);
+                      tc_wait_ld();
+#pragma unroll
+                      for (int i = 0; i < 8; ++i)
+                          unpack2f(mul2(pack2f(o0[2 * i], o0[2 * i + 1]), a2), o0[2 * i], o0[2 * i + 1]);
+                      tmem_st16(o_addr + cc * 16, o0);
+                  }
+                  tc_wait_st();
+              }
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(bar(bOS + pb));
+          }
+      }
+      __syncwarp();
+    } else if (warp < 4) {
+      reg_dealloc<kRoleRegs>();
       if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0 && nbmax > 0) {
@@ -327,6 +377,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     if (jj < skip[t]) continue;
                     const int j = jj - skip[t], pb = t * 2 + (j & 1);
                     if (!mbar_wait(bar(bPF + pb), (j >> 1) & 1, abort_flag, p.status, kWaitPFull)) { ok = false; break; }
+                    if (!mbar_wait(bar(bOS + pb), (j >> 1) & 1, abort_flag, p.status, kWaitOScaled)) { ok = false; break; }
                     TR(17, jj, 4 * t)
                     tc_fence_after();
                     if (first) {
@@ -352,7 +403,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         __syncwarp();
       }   // warp 3: no role (it completes warpgroup 0 so that it can give its registers away)
     } else {
-        reg_alloc<112>();
+        reg_alloc<104>();
         // ------------------------------------------------------------------ softmax warpgroups (4 x 4 warps)
         // Warpgroups 2 t and 2 t + 1 own query tile t; a row is shared by two threads (same lane quarter, one in
         // each warpgroup): thread `h` handles keys [64 h, 64 h + 64) of every block and columns [D/2 h, D/2 (h+1))
@@ -398,10 +449,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     tmem_st32(o_addr + cc * 32, o);
                 }
                 tc_wait_st();
+                // The correction warp rescales whole rows at block 0, and only thread 0 of a row hands the factors
+                // over: the partner's stores have to be ordered before that hand-over.
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_x);
+                alive = warp_wait(bar_x, xphase, abort_flag, p.status, kWaitPair);
+                xphase ^= 1;
+                tc_fence_after();
             }
         }
         PT_DECL
-        for (int j = 0; j < nb; ++j) {
+        for (int j = 0; alive && j < nb; ++j) {
             const int n = nb - 1 - j, pb = t * 2 + (j & 1);
             TR(warp - 4, j, 0)
             if (!warp_wait(bar(bSF + t), j & 1, abort_flag, p.status, kWaitSFull)) { alive = false; break; }
@@ -510,6 +569,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (j >= 2 && !warp_wait(bar(bPV + pb), ((j >> 1) - 1) & 1, abort_flag, p.status, kWaitPEmpty)) { alive = false; break; }
             TR(warp - 4, j, 6)
             PT(4)
+            // rescale factors to the correction warp of this lane quarter (slot j & 1 was last read for block j - 2, whose
+            // P V MMA has completed, and that MMA is issued only after the correction warp is done)
+            if (h == 0) {
+                reinterpret_cast<float*>(sgen + C::oAlpha)[((j & 1) * 2 + t) * 128 + r] = alpha;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(bAL + (t * 4 + quarter) * 2 + (j & 1)));
+            }
             // P codes: this half's two 16-byte chunks of the 64-byte-swizzled K-major row; scales: its 64-key atom
             uint8_t* prow = sgen + C::oP + pb * C::kPBytes + r * 64;
             uint32_t* sfp_row = reinterpret_cast<uint32_t*>(sgen + C::oSfP + pb * 1024 + (r & 31) * 16 + (r >> 5) * 4);
@@ -521,25 +587,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             fence_proxy_async_smem();
             TR(warp - 4, j, 7)
             PT(5)
-            // This thread's half of the O row times alpha before the block's P V is added (only when a row of the
-            // warp moved its maximum); the P V MMA of block j - 1 must have landed first
-            if ((j > 0 || carry_in) && __any_sync(0xffffffffu, alpha != 1.0f)) {
-                if (j > 0 && !warp_wait(bar(bPV + (pb ^ 1)), ((j - 1) >> 1) & 1, abort_flag, p.status, kWaitOReady)) { alive = false; break; }
-                tc_fence_after();
-                const uint64_t a2 = pack2f(alpha, alpha);
-#pragma unroll
-                for (int cc = 0; cc < D / 64; ++cc) {
-                    float o0[32];
-                    tmem_ld32(o_addr + cc * 32, o0);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        unpack2f(mul2(pack2f(o0[2 * i], o0[2 * i + 1]), a2), o0[2 * i], o0[2 * i + 1]);
-                    tmem_st32(o_addr + cc * 32, o0);
-                }
-                tc_wait_st();
-                TR(warp - 4, j, 8)
-            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(bPF + pb));
