@@ -334,6 +334,7 @@ def sageattn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlen
 
 
 _OFFLOAD_STATE: dict = {}
+_OFFLOAD_SLOTS = 2          # chunk buffers in flight (the pipeline is bound by the host link; more slots measured no gain)
 
 
 def _retire_offload_state(st) -> None:
@@ -385,8 +386,8 @@ def sageattn3_offload(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: to
     elif out.shape != q.shape or out.dtype != q.dtype or out.is_cuda:
         raise ValueError("out must be a host tensor shaped and typed like q")
     if kv_heads_per_chunk is None:
-        # about 32 chunks in total, whole kv heads per chunk, equal chunks (a divisor of Hkv)
-        target = max(1, (B * Hkv + 31) // 32)
+        # about 64 chunks in total, whole kv heads per chunk, equal chunks (a divisor of Hkv)
+        target = max(1, (B * Hkv + 63) // 64)
         kv_heads_per_chunk = max(d_ for d_ in range(1, Hkv + 1) if Hkv % d_ == 0 and d_ <= max(target, 1))
     kv_heads_per_chunk = min(kv_heads_per_chunk, Hkv)
     chunks = [(b, h0, min(h0 + kv_heads_per_chunk, Hkv)) for b in range(B) for h0 in range(0, Hkv, kv_heads_per_chunk)]
@@ -399,12 +400,12 @@ def sageattn3_offload(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: to
     # options change): allocating two chunks' worth of operands and workspace anew on every call costs more than
     # a chunk's copy.  `sageattn3_offload_release()` gives the memory back.
     state_key = (dev.index, tuple(q.shape), tuple(k.shape), q.dtype, tensor_layout, bool(is_causal), sm_scale,
-                 bool(per_block_mean), kv_heads_per_chunk)
+                 bool(per_block_mean), kv_heads_per_chunk, _OFFLOAD_SLOTS)
     st = _OFFLOAD_STATE.get("state")
     if st is None or st["key"] != state_key:
         _retire_offload_state(st)
-        st = dict(key=state_key, streams=tuple(torch.cuda.Stream(dev) for _ in range(3)), bufs=[{}, {}],
-                  comp_done=[None, None], out_done=[None, None])
+        st = dict(key=state_key, streams=tuple(torch.cuda.Stream(dev) for _ in range(3)), bufs=[{} for _ in range(_OFFLOAD_SLOTS)],
+                  comp_done=[None] * _OFFLOAD_SLOTS, out_done=[None] * _OFFLOAD_SLOTS)
         _OFFLOAD_STATE["state"] = st
     s_in, s_comp, s_out = st["streams"]
     start = torch.cuda.Event()
@@ -413,7 +414,7 @@ def sageattn3_offload(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: to
         s_.wait_event(start)
     bufs, comp_done, out_done = st["bufs"], st["comp_done"], st["out_done"]     # per slot; carried over between calls
     for i, (b, h0, h1) in enumerate(chunks):
-        slot = i & 1
+        slot = i % len(bufs)
         qh, kh, vh = cut(q, b, h0, h1, group), cut(k, b, h0, h1), cut(v, b, h0, h1)
         key = (tuple(qh.shape), tuple(kh.shape))
         with torch.cuda.stream(s_in):

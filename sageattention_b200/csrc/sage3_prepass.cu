@@ -26,6 +26,10 @@ template <> struct Num<__nv_bfloat16> {
     static __device__ __forceinline__ float2 to_f2(uint32_t w) {
         return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
     }
+    static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {     // two values rounded to T, lo in bits 0..15
+        const __nv_bfloat162 pr = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&pr);
+    }
 };
 template <> struct Num<__half> {
     using T2 = __half2;
@@ -34,6 +38,10 @@ template <> struct Num<__half> {
     static __device__ __forceinline__ __half from_f(float x) { return __float2half_rn(x); }
     static __device__ __forceinline__ float2 to_f2(uint32_t w) {
         return __half22float2(*reinterpret_cast<const __half2*>(&w));
+    }
+    static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+        const __half2 pr = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&pr);
     }
 };
 
@@ -66,6 +74,11 @@ __device__ __forceinline__ void load16_packed(const T* p, bool valid, uint4& a, 
         a = __ldg(reinterpret_cast<const uint4*>(p));
         b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
     }
+}
+// 256-bit store (32-byte aligned address): one whole sector per lane
+__device__ __forceinline__ void st_global_256(void* p, const uint32_t* w) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
 }
 template <typename T>
 __device__ __forceinline__ void unpack16(const uint4& a, const uint4& b, float* f) {   // 16 elements -> fp32
@@ -427,26 +440,53 @@ __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
             alive = __syncthreads_and(alive ? 1 : 0) != 0;
             if (!alive) break;
             tc_fence_after();
-            // epilogue: thread = query block (row), 64 keys of its row -> 128 contiguous bytes
-            const int qb = m0 + quarter * 32 + lane;
+            // epilogue: thread = query block (row) of the accumulator, 64 keys of its row = 128 contiguous bytes of delta_s
+            const uint32_t acc = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + chalf * 64;
+            if constexpr (D == 128) {
+                // The warp's 32 rows x 128 bytes go through a swizzled tile in shared memory (the A tile is free once
+                // the MMAs have completed), so that eight lanes store one whole 128-byte line.
+                uint8_t* stg = sgen + oA + warp * 4096;
 #pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {
-                float v[32];
-                tmem_ld32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + chalf * 64 + cc * 32, v);
-                tc_wait_ld();
-                if (qb < nqm) {
-                    T* drow = dh + (int64_t)qb * Np + row0 + chalf * 64 + cc * 32;
+                for (int cc = 0; cc < 2; ++cc) {
+                    float v[32];
+                    tmem_ld32(acc + cc * 32, v);
+                    tc_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         uint32_t p4[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            typename Num<T>::T2 pr;
-                            pr.x = Num<T>::from_f(v[8 * i + 2 * e]);
-                            pr.y = Num<T>::from_f(v[8 * i + 2 * e + 1]);
-                            p4[e] = *reinterpret_cast<uint32_t*>(&pr);
+                        for (int e = 0; e < 4; ++e) p4[e] = Num<T>::pack2(v[8 * i + 2 * e], v[8 * i + 2 * e + 1]);
+                        *reinterpret_cast<uint4*>(stg + lane * 128 + (((cc * 4 + i) ^ (lane & 7)) << 4)) =
+                            make_uint4(p4[0], p4[1], p4[2], p4[3]);
+                    }
+                }
+                __syncwarp();
+                const int ch = lane & 7;
+#pragma unroll
+                for (int k2 = 0; k2 < 8; ++k2) {
+                    const int row = k2 * 4 + (lane >> 3);
+                    const uint4 val = *reinterpret_cast<const uint4*>(stg + row * 128 + ((ch ^ (row & 7)) << 4));
+                    const int qb = m0 + quarter * 32 + row;
+                    if (qb < nqm) *reinterpret_cast<uint4*>(dh + (int64_t)qb * Np + row0 + chalf * 64 + ch * 8) = val;
+                }
+                __syncwarp();
+            } else {
+                // D = 64 (its A tile is too small to stage eight warps): every lane stores whole 32-byte sectors
+                const int qb = m0 + quarter * 32 + lane;
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    float v[32];
+                    tmem_ld32(acc + cc * 32, v);
+                    tc_wait_ld();
+                    if (qb < nqm) {
+                        T* drow = dh + (int64_t)qb * Np + row0 + chalf * 64 + cc * 32;
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) {
+                            uint32_t p8[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) p8[e] = Num<T>::pack2(v[16 * i + 2 * e], v[16 * i + 2 * e + 1]);
+                            st_global_256(drow + 16 * i, p8);
                         }
-                        *reinterpret_cast<uint4*>(drow + 8 * i) = make_uint4(p4[0], p4[1], p4[2], p4[3]);
                     }
                 }
             }
