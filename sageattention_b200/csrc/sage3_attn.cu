@@ -204,12 +204,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             mbar_init(bar(bPF + i), 8);    // [tile][buffer]: P (+ scales) written and O rescaled
             mbar_init(bar(bPV + i), 1);    // [tile][buffer]: the P V MMA that read it is complete
         }
-        for (int i = 0; i < 8; ++i) mbar_init(bar(bXC + i), 2);
+        for (int i = 0; i < 8; ++i) mbar_init(bar(bXC + i), 2);   // [tile][lane quarter]: both half-row warps have published a value
         // [tile][lane quarter][block parity]: the quarter's rescale factors of a block are in shared memory.  One barrier per
         // block parity: the softmax warp may publish block j + 1 before the correction warp has looked at block j, and
         // a single barrier would then be two phases ahead of the waiter.
         for (int i = 0; i < 16; ++i) mbar_init(bar(bAL + i), 1);
-        for (int i = 0; i < 4; ++i) mbar_init(bar(bOS + i), 4);   // [tile][P buffer]: the four correction warps are done with O   // [tile][lane quarter]: both half-row warps have published a value
+        for (int i = 0; i < 4; ++i) mbar_init(bar(bOS + i), 4);   // [tile][P buffer]: the four correction warps are done with O
         mbar_fence_init();
     }
     {
