@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define SAGE3_ABI_VERSION 3
+#define SAGE3_ABI_VERSION 4
 
 #if defined(__GNUC__)
 #define SAGE3_API __attribute__((visibility("default")))
@@ -124,6 +124,20 @@ SAGE3_API int sage3_prepass(const Sage3Desc* desc, const void* q, const void* k,
  * sageattention/core.py:327 does for its kernels (-inf for a row without visible keys).
  */
 SAGE3_API int sage3_attn_fwd(const Sage3Desc* desc, void* ws, void* out, float* lse, void* stream);
+
+/*
+ * Packed variable-length batch in one launch of every kernel (replaces the reference's sageattn_varlen entry,
+ * sageattention/core.py:334-448, which takes the same cu_seqlens / max_seqlen arguments).  q is [total_q][Hq][D], k and
+ * v are [total_k][Hkv][D], out is [total_q][Hq][D]; sequence b owns query rows cu_seqlens_q[b] .. cu_seqlens_q[b + 1]
+ * and key rows cu_seqlens_k[b] .. cu_seqlens_k[b + 1] (device arrays of desc->B + 1 int32, never read by the host).
+ * In `desc`: B = number of sequences, Nq / Nk = the longest query / key length (lengths beyond them are clamped),
+ * stride[1] = head stride, stride[2] = token stride, stride[0] unused.  Every sequence is smoothed, quantized and
+ * attended exactly as a sage3_fwd call on it alone would be (its own K mean, its own padding to 128 rows, causal mask
+ * aligned on its own lengths); a sequence without keys gets zeros.  The workspace is the one of a uniform batch of B
+ * entries of the maximum lengths (sage3_workspace_bytes(desc)).  No LSE output, no per-call K mean, no carried state.
+ */
+SAGE3_API int sage3_fwd_varlen(const Sage3Desc* desc, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, const void* q,
+                               const void* k, const void* v, void* out, void* ws, void* stream);
 
 /*
  * sage3_prepass with the K mean supplied by the caller: `km` is a device array dtype[B][Hkv][D] that is used instead of

@@ -12,7 +12,7 @@ _PKG = pathlib.Path(__file__).resolve().parent
 LIB_PATH = _PKG / "libsage3_b200.so"
 
 SAGE3_FP16, SAGE3_BF16 = 0, 1
-ABI_VERSION = 3          # SAGE3_ABI_VERSION of include/sage3_b200.h this module's structs were written for
+ABI_VERSION = 4          # SAGE3_ABI_VERSION of include/sage3_b200.h this module's structs were written for
 SAGE3_OK = 0
 SAGE3_E_DEVICE_WAIT = -9
 
@@ -98,6 +98,8 @@ def lib() -> C.CDLL:
     l.sage3_shared_free.argtypes = [V]
     l.sage3_fwd.restype = C.c_int
     l.sage3_fwd.argtypes = [P(Sage3Desc), V, V, V, V, V, V, V]
+    l.sage3_fwd_varlen.restype = C.c_int
+    l.sage3_fwd_varlen.argtypes = [P(Sage3Desc), V, V, V, V, V, V, V, V]
     l.sage3_selftest_wait_timeout.restype = C.c_int
     l.sage3_selftest_wait_timeout.argtypes = [V, V]
     l.sage3_slab_copy.restype = C.c_int
@@ -115,7 +117,7 @@ def lib() -> C.CDLL:
 EXPORTED = ["sage3_version", "sage3_strerror", "sage3_workspace_layout", "sage3_workspace_bytes", "sage3_prepass",
             "sage3_attn_fwd", "sage3_fwd", "sage3_check_status", "sage3_kmean_noalloc", "sage3_selftest_wait_timeout", "sage3_slab_copy", "sage3_merge_partial",
             "sage3_prepass_kmean", "sage3_prepass_parts", "sage3_attn_fwd_parts", "sage3_attn_fwd_carry", "sage3_shared_alloc", "sage3_shared_open",
-            "sage3_shared_close", "sage3_shared_free"]
+            "sage3_shared_close", "sage3_shared_free", "sage3_fwd_varlen"]
 
 
 def check(code: int, where: str) -> None:

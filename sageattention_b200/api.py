@@ -305,31 +305,83 @@ def sageattn(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, retur
 
 def sageattn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q, cu_seqlens_k,
                     max_seqlen_q: int | None = None, max_seqlen_k: int | None = None, is_causal: bool = False,
-                    sm_scale=None, **kwargs) -> torch.Tensor:
+                    sm_scale=None, per_block_mean: bool = True, **kwargs) -> torch.Tensor:
     """Signature of the reference's packed variable-length entry (sageattention/core.py:334-345): q
     [total_q, Hq, D], k, v [total_k, Hkv, D]; sequence i owns rows cu_seqlens[i]:cu_seqlens[i+1].  Returns
-    [total_q, Hq, D].  Smoothing means are per sequence, so every sequence is one call of the FP4 path on its slice
-    (addressed through strides, nothing is copied); `max_seqlen_*` and `smooth_k` are accepted for compatibility."""
+    [total_q, Hq, D].
+
+    The whole batch is ONE launch of every kernel (`sage3_fwd_varlen`): the kernels read cu_seqlens on the device, every
+    sequence is smoothed, quantized and attended exactly as a call on it alone would be, and a sequence without keys
+    gets zeros.  With `max_seqlen_q` / `max_seqlen_k` given and cu_seqlens already int32 CUDA tensors the call does not
+    synchronize with the device; without them the maxima are read from cu_seqlens (one device-to-host copy).  Scratch is
+    sized for `number of sequences x maximum lengths`.  `smooth_k` is accepted for compatibility; a scalar `sm_scale`
+    only."""
     if q.dim() != 3 or k.dim() != 3 or v.dim() != 3:
         raise ValueError("q, k, v must be packed as [tokens, heads, head_dim]")
-    cq = [int(x) for x in (cu_seqlens_q.tolist() if isinstance(cu_seqlens_q, torch.Tensor) else cu_seqlens_q)]
-    ck = [int(x) for x in (cu_seqlens_k.tolist() if isinstance(cu_seqlens_k, torch.Tensor) else cu_seqlens_k)]
-    if len(cq) != len(ck) or len(cq) < 2 or cq[0] != 0 or ck[0] != 0 or cq[-1] != q.shape[0] or ck[-1] != k.shape[0]:
-        raise ValueError("cu_seqlens_q / cu_seqlens_k must start at 0, end at the token counts and have equal length")
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} must be a CUDA tensor: sageattention_b200 has no CPU path")
+    if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise TypeError("q, k, v must share dtype torch.float16 or torch.bfloat16")
+    if k.shape != v.shape or k.shape[2] != q.shape[2]:
+        raise ValueError("k and v must have one shape and the head dim of q")
+    if isinstance(sm_scale, torch.Tensor):
+        raise ValueError("sageattn_varlen takes a scalar sm_scale")
     kwargs.pop("smooth_k", None)
-    out = torch.empty_like(q)
-    for i in range(len(cq) - 1):
-        q0, q1, k0, k1 = cq[i], cq[i + 1], ck[i], ck[i + 1]
-        if q1 == q0:
-            continue
-        if k1 == k0:
-            out[q0:q1].zero_()
-            continue
-        qi, ki, vi = q[q0:q1].unsqueeze(0), k[k0:k1].unsqueeze(0), v[k0:k1].unsqueeze(0)
-        pbm = kwargs.get("per_block_mean", True)
-        prob = Sage3Problem(qi, ki, vi, "NHD", is_causal, sm_scale, pbm, out=out[q0:q1].unsqueeze(0),
-                            workspace=_cached_workspace(qi, ki, "NHD", pbm))
-        prob.run()
+    dev = q.device
+    Hq, Hkv, D = q.shape[1], k.shape[1], q.shape[2]
+    if D not in (64, 128):
+        raise ValueError(f"head dim must be 64 or 128, got {D}")
+    if Hq % Hkv != 0:
+        raise ValueError(f"number of query heads ({Hq}) must be a multiple of kv heads ({Hkv})")
+
+    def as_cu(x):
+        t = x if isinstance(x, torch.Tensor) else torch.tensor(list(x), dtype=torch.int32)
+        return t.to(device=dev, dtype=torch.int32).contiguous()
+    cq, ck = as_cu(cu_seqlens_q), as_cu(cu_seqlens_k)
+    if cq.dim() != 1 or cq.shape != ck.shape or cq.numel() < 2:
+        raise ValueError("cu_seqlens_q / cu_seqlens_k must be 1-D, of equal length >= 2")
+    nseq = cq.numel() - 1
+    if max_seqlen_q is None or max_seqlen_k is None:
+        # the one place that looks at the lengths on the host (and checks them while it is at it)
+        hq, hk = cq.tolist(), ck.tolist()
+        if hq[0] != 0 or hk[0] != 0 or hq[-1] != q.shape[0] or hk[-1] != k.shape[0] or \
+                any(b < a for a, b in zip(hq, hq[1:])) or any(b < a for a, b in zip(hk, hk[1:])):
+            raise ValueError("cu_seqlens_q / cu_seqlens_k must start at 0, be non-decreasing and end at the token counts")
+        max_seqlen_q = max(b - a for a, b in zip(hq, hq[1:]))
+        max_seqlen_k = max(b - a for a, b in zip(hk, hk[1:]))
+    out = torch.empty_like(q if _usable(q) else q.contiguous())
+    if q.shape[0] == 0:
+        return out
+    max_seqlen_q, max_seqlen_k = max(int(max_seqlen_q), 1), max(int(max_seqlen_k), 1)
+    qc, kc, vc = (t if _usable(t) else t.contiguous() for t in (q, k, v))
+    d = _cabi.Sage3Desc()
+    d.B, d.Hq, d.Hkv, d.Nq, d.Nk, d.D = nseq, Hq, Hkv, max_seqlen_q, max_seqlen_k, D
+    d.dtype = _DTYPES[q.dtype]
+    d.is_causal = int(bool(is_causal))
+    d.per_block_mean = int(bool(per_block_mean))
+    d.q_stride = (C.c_int64 * 3)(0, qc.stride(1), qc.stride(0))
+    d.k_stride = (C.c_int64 * 3)(0, kc.stride(1), kc.stride(0))
+    d.v_stride = (C.c_int64 * 3)(0, vc.stride(1), vc.stride(0))
+    d.o_stride = (C.c_int64 * 3)(0, out.stride(1), out.stride(0))
+    if sm_scale is not None:
+        d.sm_scale = float(sm_scale)
+        if not d.sm_scale > 0:
+            raise ValueError("sm_scale must be positive")
+    need = _cabi.lib().sage3_workspace_bytes(C.byref(d))
+    if need == 0:
+        raise ValueError("sageattn_varlen: shape not supported (see sage3_workspace_layout)")
+    key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+    buf = _WORKSPACES.get(key)
+    if buf is None or buf.numel() < need + 256:
+        _WORKSPACES.pop(key, None)
+        buf = torch.empty(need + 256, dtype=torch.uint8, device=dev)
+        _WORKSPACES[key] = buf
+    shift = (-buf.data_ptr()) % 256
+    with torch.cuda.device(dev):
+        _cabi.check(_cabi.lib().sage3_fwd_varlen(C.byref(d), cq.data_ptr(), ck.data_ptr(), qc.data_ptr(), kc.data_ptr(),
+                                                 vc.data_ptr(), out.data_ptr(), buf.data_ptr() + shift,
+                                                 torch.cuda.current_stream(dev).cuda_stream), "sage3_fwd_varlen")
     return out
 
 

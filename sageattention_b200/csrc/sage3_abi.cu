@@ -103,7 +103,7 @@ sage3::PartsPtr one_part(const void* p) {
 }
 
 int attn_impl(const Sage3Desc* desc, void* ws, const sage3::PartsPtr& out, float* lse, float* debug, void* stream,
-              const Sage3Carry* carry = nullptr) {
+              const Sage3Carry* carry = nullptr, const int32_t* cu_q = nullptr, const int32_t* cu_k = nullptr) {
     Sage3Workspace w;
     int rc = layout(desc, &w);
     if (rc != SAGE3_OK) return rc;
@@ -145,6 +145,7 @@ int attn_impl(const Sage3Desc* desc, void* ws, const sage3::PartsPtr& out, float
     a.causal_shift = (carry && carry->use_causal_shift) ? carry->causal_shift : desc->Nk - desc->Nq;
     a.status = reinterpret_cast<int*>(base + w.status) + kAttnStatusWord;
     a.prepass_status = reinterpret_cast<const int*>(base + w.status);
+    a.cu_q = cu_q; a.cu_k = cu_k;
 #ifdef SAGE3_DEV_TRACE
     a.debug = debug;
 #else
@@ -268,7 +269,7 @@ SAGE3_API size_t sage3_workspace_bytes(const Sage3Desc* desc) {
 }
 
 static int prepass_impl(const Sage3Desc* desc, const sage3::PartsPtr& q, const sage3::PartsPtr& k, const sage3::PartsPtr& v,
-                        const void* km_in, void* ws, void* stream) {
+                        const void* km_in, void* ws, void* stream, const int32_t* cu_q = nullptr, const int32_t* cu_k = nullptr) {
     Sage3Workspace w;
     int rc = layout(desc, &w);
     if (rc != SAGE3_OK) return rc;
@@ -297,6 +298,7 @@ static int prepass_impl(const Sage3Desc* desc, const sage3::PartsPtr& q, const s
     a.v_codes = base + w.v_codes; a.v_sf = base + w.v_sf;
     a.qkm = reinterpret_cast<float*>(base + w.qkm);
     a.status = reinterpret_cast<int*>(base + w.status);
+    a.cu_q = cu_q; a.cu_k = cu_k;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (cudaMemsetAsync(base + w.status, 0, kStatusWords * sizeof(int32_t), st) != cudaSuccess) return SAGE3_E_CUDA;
     a.km_given = km_in != nullptr;
@@ -310,6 +312,18 @@ SAGE3_API int sage3_prepass(const Sage3Desc* desc, const void* q, const void* k,
     if (!q || !k || !v) return SAGE3_E_NULL;
     if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16)) return SAGE3_E_ALIGN;
     return prepass_impl(desc, one_part(q), one_part(k), one_part(v), nullptr, ws, stream);
+}
+
+// Packed variable-length batch: desc->B sequences, desc->Nq / desc->Nk the longest of them, sequence b owning rows
+// cu[b] .. cu[b + 1] of the packed tensors.  One launch of every kernel covers the whole batch; the workspace has the
+// layout of a uniform batch of the maximum lengths, and CTAs beyond a sequence's own length leave at once.
+SAGE3_API int sage3_fwd_varlen(const Sage3Desc* desc, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, const void* q,
+                               const void* k, const void* v, void* out, void* ws, void* stream) {
+    if (!desc || !cu_seqlens_q || !cu_seqlens_k || !q || !k || !v || !out) return SAGE3_E_NULL;
+    if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(cu_seqlens_q, 4) || !aligned(cu_seqlens_k, 4)) return SAGE3_E_ALIGN;
+    const int rc = prepass_impl(desc, one_part(q), one_part(k), one_part(v), nullptr, ws, stream, cu_seqlens_q, cu_seqlens_k);
+    if (rc != SAGE3_OK) return rc;
+    return attn_impl(desc, ws, one_part(out), nullptr, nullptr, stream, nullptr, cu_seqlens_q, cu_seqlens_k);
 }
 
 SAGE3_API int sage3_prepass_kmean(const Sage3Desc* desc, const void* q, const void* k, const void* v, const void* km, void* ws,

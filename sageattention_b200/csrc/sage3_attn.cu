@@ -87,6 +87,7 @@ struct AttnParams {
     const float *carry_o_in, *carry_m_in, *carry_l_in;   // fp32 [B*Hq][Nq][D] unnormalized O; [B*Hq][Nq] running max; [B*Hq][Nq][2] partial row sums
     float *carry_o_out, *carry_m_out, *carry_l_out;
     int causal_shift;                   // key j is visible to query i iff j <= i + causal_shift
+    const int *cu_q, *cu_k;             // packed variable-length sequences (VARLEN kernels): entry b owns rows cu[b] .. cu[b + 1]
 #ifdef SAGE3_DEV_TRACE
     float* debug;                       // development dump of CTA 0 (nullptr in normal use)
 #endif
@@ -143,7 +144,7 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
     return __all_sync(0xffffffffu, ok);
 }
 
-template <int D, bool CAUSAL, typename OutT>
+template <int D, bool CAUSAL, typename OutT, bool VARLEN>
 __global__ void __launch_bounds__(Cfg<D>::kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p) {
@@ -168,19 +169,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     int pr = blockIdx.x % npair;
     if (CAUSAL) pr = npair - 1 - pr;
     const int mt0 = 2 * pr;
-    const int nv = (mt0 + 1 < p.nqt) ? 2 : 1;            // query tiles this CTA really has
     const int b = bhq / p.Hq, hq = bhq % p.Hq;
     const int bhkv = b * p.Hkv + hq / (p.Hq / p.Hkv);
-    const int shift = p.causal_shift;
+    // Lengths of this batch entry.  p.Nq, p.Nk, p.nqt, p.nkb stay the strides of the workspace layouts; with packed
+    // variable-length sequences they are the maxima and the entry's own lengths come from the cu arrays.
+    int Nq = p.Nq, Nk = p.Nk, nqt = p.nqt, nkb = p.nkb, shift = p.causal_shift;
+    int64_t out_base = b * p.os0;
+    if constexpr (VARLEN) {
+        const int q0 = p.cu_q[b], k0 = p.cu_k[b];
+        Nq = min(max(p.cu_q[b + 1] - q0, 0), p.Nq);
+        Nk = min(max(p.cu_k[b + 1] - k0, 0), p.Nk);
+        nqt = (Nq + kBlock - 1) / kBlock;
+        nkb = (Nk + kBlock - 1) / kBlock;
+        shift = Nk - Nq;
+        out_base = (int64_t)q0 * p.os2;
+    }
+    const int nv = (mt0 + 1 < nqt) ? 2 : (VARLEN && mt0 >= nqt ? 0 : 1);   // query tiles this CTA really has
     // an earlier CTA of this launch gave up, or the pre-pass did (the workspace is then incomplete)
     const bool dead_launch = (*reinterpret_cast<volatile int*>(p.status) != 0) || (*reinterpret_cast<const volatile int*>(p.prepass_status) != 0);
     // KV blocks of tile t: [0, nbt[t]); the CTA walks block n = nbmax - 1 ... 0 and tile t joins at step skip[t]
     int nbt[2];
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
-        int nb = p.nkb;
+        int nb = nkb;
         if (CAUSAL) {
-            const int max_key = min(p.Nk - 1, (mt0 + t) * kBlock + kBlock - 1 + shift);
+            const int max_key = min(Nk - 1, (mt0 + t) * kBlock + kBlock - 1 + shift);
             nb = max_key < 0 ? 0 : max_key / kBlock + 1;
         }
         nbt[t] = (dead_launch || t >= nv) ? 0 : nb;
@@ -433,7 +446,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const size_t crow = (size_t)bhq * p.Nq + grow;           // row of the carried state
         if (carry_in && t < nv && !dead_launch) {
             // resume: the accumulator continues from the state an earlier call left (its key range came later in the walk)
-            const bool live = grow < p.Nq;
+            const bool live = grow < Nq;
             m_run = live ? p.carry_m_in[crow] : -INFINITY;
             l_run = live ? p.carry_l_in[2 * crow + h] : 0.f;          // each of the row's two threads keeps its own partial sum
             if (nb > 0) {
@@ -476,9 +489,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (lane == 0) mbar_arrive(bar(bSE));     // S is in registers: the other tile's Q K^T may overwrite it
             TR(warp - 4, j, 2)
             PT(1)
-            const bool need_mask = ((n + 1) * kBlock > p.Nk) || (CAUSAL && (n * kBlock + kBlock - 1 > mt * kBlock + shift));
+            const bool need_mask = ((n + 1) * kBlock > Nk) || (CAUSAL && (n * kBlock + kBlock - 1 > mt * kBlock + shift));
             if (need_mask) {
-                int lim = p.Nk - 1;
+                int lim = Nk - 1;
                 if (CAUSAL) lim = min(lim, grow + shift);
                 const int key0 = n * kBlock + 64 * h;
 #pragma unroll
@@ -607,7 +620,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 alive = warp_wait(bar(bPV + t * 2 + ((nb - 1) & 1)), ((nb - 1) >> 1) & 1, abort_flag, p.status, kWaitOReady);
                 tc_fence_after();
             }
-            if (alive && p.lse != nullptr && h == 0 && grow < p.Nq) {
+            if (alive && p.lse != nullptr && h == 0 && grow < Nq) {
                 // ln sum_k exp(scale * q.k): the kernel's row sum is 2688 * sum_k 2^((S_k - m) s) over the smoothed
                 // scores S (delta_s included); K smoothing took scale * q.km out of every score of the row
                 const float ms_fin = (m_run == -INFINITY ? 0.f : m_run) * sl2;
@@ -623,8 +636,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 // output goes straight back to the token shards of a sequence-parallel group: plain stores)
                 const int opart = (p.out_rows == 0) ? 0 : min(grow / p.out_rows, kMaxParts - 1);
                 const int orow_l = grow - opart * p.out_rows;
-                OutT* orow = static_cast<OutT*>(p.out[opart]) + b * p.os0 + hq * p.os1 + (int64_t)orow_l * p.os2 + (D / 2) * h;
-                if (p.carry_o_out != nullptr && grow < p.Nq) {
+                OutT* orow = static_cast<OutT*>(p.out[opart]) + out_base + hq * p.os1 + (int64_t)orow_l * p.os2 + (D / 2) * h;
+                if (p.carry_o_out != nullptr && grow < Nq) {
                     if (h == 0) p.carry_m_out[crow] = m_run;
                     p.carry_l_out[2 * crow + h] = l_run;
                 }
@@ -634,7 +647,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     if (nb > 0) {
                         tmem_ld32(o_addr + cc * 32, o);
                         tc_wait_ld();
-                    } else if (carry_in && grow < p.Nq) {
+                    } else if (carry_in && grow < Nq) {
                         // no key block of this call is visible to the tile: the state passes through
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
@@ -649,13 +662,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                         for (int i = 0; i < 32; ++i) p.debug[16384 + 512 + r * D + (D / 2) * h + cc * 32 + i] = o[i];
                         if (cc == 0 && h == 0) p.debug[16384 + 384 + r] = l_tot;
                     })
-                    if (p.carry_o_out != nullptr && grow < p.Nq) {
+                    if (p.carry_o_out != nullptr && grow < Nq) {
 #pragma unroll
                         for (int i = 0; i < 8; ++i)
                             *reinterpret_cast<float4*>(p.carry_o_out + crow * D + (D / 2) * h + cc * 32 + 4 * i) =
                                 make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
                     }
-                    if (want_out && grow < p.Nq) {
+                    if (want_out && grow < Nq) {
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             uint4 w;
@@ -717,15 +730,23 @@ static CUresult make_map(EncodeTiledFn fn, CUtensorMap* m, const void* base, uin
               CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 }
 
-template <int D, bool CAUSAL, typename OutT>
-static cudaError_t launch_t(const AttnArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+template <int D, bool CAUSAL, typename OutT, bool VARLEN>
+static cudaError_t launch_v(const AttnArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                             const AttnParams& p, cudaStream_t st) {
-    auto kern = attn_fwd_kernel<D, CAUSAL, OutT>;
+    auto kern = attn_fwd_kernel<D, CAUSAL, OutT, VARLEN>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes);
     if (e != cudaSuccess) return e;
     const int grid = a.B * a.Hq * ((a.Nq_p / kBlock + 1) / 2);      // one CTA per pair of query tiles
     kern<<<grid, Cfg<D>::kThreads, Cfg<D>::kSmemBytes, st>>>(tq, tk, tv, p);
     return cudaGetLastError();
+}
+
+template <int D, bool CAUSAL, typename OutT>
+static cudaError_t launch_t(const AttnArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                            const AttnParams& p, cudaStream_t st) {
+    // packed variable-length batches run their own instantiation, so that the uniform kernels carry none of it
+    return a.cu_q != nullptr ? launch_v<D, CAUSAL, OutT, true>(a, tq, tk, tv, p, st)
+                             : launch_v<D, CAUSAL, OutT, false>(a, tq, tk, tv, p, st);
 }
 
 cudaError_t launch_attn(const AttnArgs& a, cudaStream_t st, int* driver_rc) {
@@ -759,6 +780,7 @@ cudaError_t launch_attn(const AttnArgs& a, cudaStream_t st, int* driver_rc) {
     p.carry_o_in = a.carry_o_in; p.carry_m_in = a.carry_m_in; p.carry_l_in = a.carry_l_in;
     p.carry_o_out = a.carry_o_out; p.carry_m_out = a.carry_m_out; p.carry_l_out = a.carry_l_out;
     p.causal_shift = a.causal_shift;
+    p.cu_q = a.cu_q; p.cu_k = a.cu_k;
 #ifdef SAGE3_DEV_TRACE
     p.debug = a.debug;
 #endif

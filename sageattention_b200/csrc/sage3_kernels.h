@@ -29,6 +29,9 @@ struct PrepassArgs {
     uint8_t *q_codes, *q_sf, *k_codes, *k_sf, *v_codes, *v_sf;
     float* qkm;                    // fp32 [B][Hq][Nq_p]: q . km per query row
     int* status;                   // device status words (bounded waits report here)
+    // packed variable-length sequences (both nullptr: every batch entry has Nq / Nk tokens): device int32 [B + 1], entry b
+    // owns rows cu[b] .. cu[b + 1] of the packed tensor; Nq / Nk are then the maximum lengths, stride 0 is unused
+    const int *cu_q, *cu_k;
 };
 
 struct AttnArgs {
@@ -48,6 +51,7 @@ struct AttnArgs {
     float *carry_o_out, *carry_m_out, *carry_l_out;
     int causal_shift;               // key j visible to query i iff j <= i + causal_shift (Nk - Nq unless the caller offsets it)
     const int* prepass_status;      // the pre-pass's status word (non-zero: the workspace is incomplete, do nothing)
+    const int *cu_q, *cu_k;         // packed variable-length sequences, as in PrepassArgs (nullptr: uniform lengths)
 #ifdef SAGE3_DEV_TRACE
     float* debug;                   // development dump of the first CTA; nullptr in normal use
 #endif

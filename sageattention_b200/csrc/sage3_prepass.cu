@@ -50,6 +50,16 @@ template <typename T>
 struct Src {
     const T* part[kMaxParts];
     int rows;                       // tokens per part; 0 = everything in part[0]
+    const int* cu;                  // packed variable-length sequences: batch entry b owns rows cu[b] .. cu[b + 1]; nullptr: uniform
+    // Element offset of (batch entry b, head h); with `cu` also replaces N (the maximum length) by the entry's own length.
+    __device__ __forceinline__ int64_t base(int b, int h, int64_t sb, int64_t sh, int64_t sn, int& N) const {
+        if (cu != nullptr) {
+            const int r0 = cu[b];
+            N = min(max(cu[b + 1] - r0, 0), N);
+            return (int64_t)r0 * sn + h * sh;
+        }
+        return b * sb + h * sh;
+    }
     __device__ __forceinline__ const T* row(int64_t bh_off, int r, int64_t sn) const {
         if (rows == 0) return part[0] + bh_off + (int64_t)r * sn;
         const int pi = min(r / rows, kMaxParts - 1);
@@ -57,10 +67,11 @@ struct Src {
     }
 };
 template <typename T>
-static Src<T> make_src(const PartsPtr& a) {
+static Src<T> make_src(const PartsPtr& a, const int* cu = nullptr) {
     Src<T> s;
     for (int i = 0; i < kMaxParts; ++i) s.part[i] = static_cast<const T*>(a.base[i]);
     s.rows = a.rows;
+    s.cu = cu;
     return s;
 }
 
@@ -113,12 +124,12 @@ __device__ __forceinline__ void quant16(const float* x, uint32_t& lo, uint32_t& 
 template <typename T, int D>
 __global__ void __launch_bounds__(256) colsum_partial_kernel(const __grid_constant__ Src<T> x, int64_t sb, int64_t sh,
                                                              int64_t sn, int H, int N,
-                                                             float* __restrict__ part, int chunks) {
+                                                             float* __restrict__ part, int chunks) {   // N: by value, narrowed per entry
     constexpr int TPR = D / 8;           // threads per row (8 elements = 16 bytes each)
     constexpr int RPP = 256 / TPR;       // rows per pass
     const int chunk = blockIdx.x, bh = blockIdx.y;
     const int b = bh / H, h = bh % H;
-    const int64_t bh_off = b * sb + h * sh;
+    const int64_t bh_off = x.base(b, h, sb, sh, sn, N);
     const int c8 = threadIdx.x % TPR, rl = threadIdx.x / TPR;
     const int r0 = chunk * kRowsPerChunk;
     const int r1 = min(N, r0 + kRowsPerChunk);
@@ -147,8 +158,15 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(const __grid_consta
 
 template <typename T, int D>
 __global__ void colmean_finalize_kernel(const float* __restrict__ part, int chunks, float inv_count,
-                                        T* __restrict__ mean) {
+                                        T* __restrict__ mean, const int* __restrict__ cu, int H, int pad_to_block) {
     const int bh = blockIdx.x, d = threadIdx.x;
+    if (cu != nullptr) {
+        // the entry's own token count (rounded up to whole 128-row blocks where the mean is over the padded rows);
+        // chunks beyond it hold zeros, so the sum is the one a call on this entry alone would form
+        int n = max(cu[bh / H + 1] - cu[bh / H], 0);
+        if (pad_to_block) n = (n + kBlock - 1) / kBlock * kBlock;
+        inv_count = n > 0 ? 1.0f / (float)n : 0.f;
+    }
     float s = 0.f;
     for (int c = 0; c < chunks; ++c) s += part[((int64_t)bh * chunks + c) * D + d];
     mean[(int64_t)bh * D + d] = Num<T>::from_f(s * inv_count);
@@ -177,8 +195,9 @@ __global__ void __launch_bounds__(256, 3) quant_rows_kernel(
     const int b = bh / H, h = bh % H;
     const int t = threadIdx.x;
     const int c = t % CH, rl = t / CH;
-    const int64_t bh_off = b * sb + h * sh;
+    const int64_t bh_off = x.base(b, h, sb, sh, sn, N);
     const int row0 = tile * kBlock;
+    if (row0 >= N && row0 > 0) return;    // a tile beyond this entry's padded length (variable-length batches only)
 
     extern __shared__ __align__(16) uint8_t smem_raw[];
     float* s_mean = reinterpret_cast<float*>(smem_raw);                        // [D]
@@ -320,7 +339,7 @@ __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
     uint8_t* __restrict__ sfs,         // [B*H][Np/128][D/64][512]
     const T* __restrict__ qm_all,      // [B][Hq][nqm][D]
     T* __restrict__ delta,             // [B][Hq][nqm][Np]
-    int Hq, int nqm, int* __restrict__ status) {
+    int Hq, int nqm, int* __restrict__ status, const int* __restrict__ cu_q) {
     constexpr int CH = D / 16;            // microblocks per row
     constexpr int RPP = 256 / CH;         // rows per pass
     constexpr int ITEMS = kBlock / RPP;   // microblocks per thread
@@ -332,8 +351,11 @@ __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
     const int b = bh / H, h = bh % H;
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int c = t % CH, rl = t / CH;
-    const int64_t bh_off = b * sb + h * sh;
+    const int64_t bh_off = x.base(b, h, sb, sh, sn, N);
     const int row0 = tile * kBlock;
+    if (row0 >= N && row0 > 0) return;    // a tile beyond this entry's padded length (variable-length batches only)
+    // query blocks this entry really has (nqm stays the row count of the qm / delta_s layouts)
+    const int nqm_live = (cu_q != nullptr) ? min(nqm, (max(cu_q[b + 1] - cu_q[b], 0) + kBlock - 1) / kBlock) : nqm;
 
     extern __shared__ uint8_t smem_dyn[];
     const uint32_t sbase = (smem_u32(smem_dyn) + 1023u) & ~1023u;
@@ -415,12 +437,12 @@ __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
         const int hq = h * group + g;
         const T* qmh = qm_all + ((int64_t)b * Hq + hq) * nqm * D;
         T* dh = delta + ((int64_t)b * Hq + hq) * nqm * (int64_t)Np;
-        for (int m0 = 0; m0 < nqm && alive; m0 += 128, ++iter) {
+        for (int m0 = 0; m0 < nqm_live && alive; m0 += 128, ++iter) {
             // A tile: 128 query-block means, same swizzled layout
             for (int idx = t; idx < 128 * (D / 8); idx += 256) {
                 const int r = idx / (D / 8), chunk = idx % (D / 8);
                 uint4 val = make_uint4(0, 0, 0, 0);
-                if (m0 + r < nqm) val = __ldg(reinterpret_cast<const uint4*>(qmh + (int64_t)(m0 + r) * D + chunk * 8));
+                if (m0 + r < nqm_live) val = __ldg(reinterpret_cast<const uint4*>(qmh + (int64_t)(m0 + r) * D + chunk * 8));
                 *reinterpret_cast<uint4*>(sgen + oA + (chunk >> 3) * 16384 + r * 128 + (((chunk & 7) ^ (r & 7)) << 4)) = val;
             }
             fence_proxy_async_smem();
@@ -467,7 +489,7 @@ __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
                     const int row = k2 * 4 + (lane >> 3);
                     const uint4 val = *reinterpret_cast<const uint4*>(stg + row * 128 + ((ch ^ (row & 7)) << 4));
                     const int qb = m0 + quarter * 32 + row;
-                    if (qb < nqm) *reinterpret_cast<uint4*>(dh + (int64_t)qb * Np + row0 + chalf * 64 + ch * 8) = val;
+                    if (qb < nqm_live) *reinterpret_cast<uint4*>(dh + (int64_t)qb * Np + row0 + chalf * 64 + ch * 8) = val;
                 }
                 __syncwarp();
             } else {
@@ -478,7 +500,7 @@ __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
                     float v[32];
                     tmem_ld32(acc + cc * 32, v);
                     tc_wait_ld();
-                    if (qb < nqm) {
+                    if (qb < nqm_live) {
                         T* drow = dh + (int64_t)qb * Np + row0 + chalf * 64 + cc * 32;
 #pragma unroll
                         for (int i = 0; i < 2; ++i) {
@@ -513,8 +535,9 @@ __global__ void __launch_bounds__(256) quant_vt_kernel(const __grid_constant__ S
     const int tile = blockIdx.x, bh = blockIdx.y;
     const int b = bh / H, h = bh % H;
     const int t = threadIdx.x;
-    const int64_t bh_off = b * sb + h * sh;
+    const int64_t bh_off = x.base(b, h, sb, sh, sn, N);
     const int row0 = tile * kBlock;
+    if (row0 >= N && row0 > 0) return;    // a tile beyond this entry's padded length (variable-length batches only)
 
     extern __shared__ __align__(16) uint8_t smem_raw[];
     T* s_v = reinterpret_cast<T*>(smem_raw);                                  // [128][PITCH]
@@ -571,7 +594,7 @@ __global__ void __launch_bounds__(256) quant_vt_kernel(const __grid_constant__ S
 // ------------------------------------------------------------------------------------------------
 template <typename T, int D>
 static cudaError_t launch_prepass_t(const PrepassArgs& a, cudaStream_t st) {
-    const Src<T> q = make_src<T>(a.q), k = make_src<T>(a.k), v = make_src<T>(a.v);
+    const Src<T> q = make_src<T>(a.q, a.cu_q), k = make_src<T>(a.k, a.cu_k), v = make_src<T>(a.v, a.cu_k);
     T* km = static_cast<T*>(a.km);
     T* qm = static_cast<T*>(a.qm);
     T* delta = static_cast<T*>(a.delta);
@@ -581,7 +604,7 @@ static cudaError_t launch_prepass_t(const PrepassArgs& a, cudaStream_t st) {
     if (!a.km_given) {
         colsum_partial_kernel<T, D><<<dim3(a.kchunks_k, BHkv), 256, 0, st>>>(k, a.ks[0], a.ks[1], a.ks[2], a.Hkv, a.Nk,
                                                                              a.kpart, a.kchunks_k);
-        colmean_finalize_kernel<T, D><<<BHkv, D, 0, st>>>(a.kpart, a.kchunks_k, 1.0f / (float)a.Nk, km);
+        colmean_finalize_kernel<T, D><<<BHkv, D, 0, st>>>(a.kpart, a.kchunks_k, 1.0f / (float)a.Nk, km, a.cu_k, a.Hkv, 0);
     }
 
     const size_t smem_q = D * 4 + (D / 64) * 512;
@@ -595,7 +618,7 @@ static cudaError_t launch_prepass_t(const PrepassArgs& a, cudaStream_t st) {
         // consumed it and stream order serializes the two uses
         colsum_partial_kernel<T, D><<<dim3(a.kchunks_q, BHq), 256, 0, st>>>(q, a.qs[0], a.qs[1], a.qs[2], a.Hq, a.Nq,
                                                                             a.kpart, a.kchunks_q);
-        colmean_finalize_kernel<T, D><<<BHq, D, 0, st>>>(a.kpart, a.kchunks_q, 1.0f / (float)a.Nq_p, qm);
+        colmean_finalize_kernel<T, D><<<BHq, D, 0, st>>>(a.kpart, a.kchunks_q, 1.0f / (float)a.Nq_p, qm, a.cu_q, a.Hq, 1);
         quant_rows_kernel<T, D, kModeQGlobalMean><<<dim3(a.Nq_p / kBlock, BHq), 256, smem_q, st>>>(
             q, a.qs[0], a.qs[1], a.qs[2], a.Hq, a.Nq, a.Nq_p, qm, nullptr, a.q_codes, a.q_sf, km, a.Hq / a.Hkv, a.qkm);
     }
@@ -603,7 +626,7 @@ static cudaError_t launch_prepass_t(const PrepassArgs& a, cudaStream_t st) {
     cudaError_t e = cudaFuncSetAttribute(quant_k_delta_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_k);
     if (e != cudaSuccess) return e;
     quant_k_delta_kernel<T, D><<<dim3(a.Nk_p / kBlock, BHkv), 256, smem_k, st>>>(
-        k, a.ks[0], a.ks[1], a.ks[2], a.Hkv, a.Nk, a.Nk_p, km, a.k_codes, a.k_sf, qm, delta, a.Hq, a.nqm, a.status);
+        k, a.ks[0], a.ks[1], a.ks[2], a.Hkv, a.Nk, a.Nk_p, km, a.k_codes, a.k_sf, qm, delta, a.Hq, a.nqm, a.status, a.cu_q);
 
     const size_t smem_v = ((kBlock * (D + 2) * sizeof(T) + 15) / 16) * 16 + D * 72 + 1024;
     e = cudaFuncSetAttribute(quant_vt_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_v);
@@ -658,7 +681,7 @@ cudaError_t launch_kmean_t(const Sage3Desc* d, const void* k, void* km, float* s
     one.base[0] = const_cast<void*>(k);
     sage3::colsum_partial_kernel<T, D><<<dim3(chunks, BH), 256, 0, st>>>(
         sage3::make_src<T>(one), d->k_stride[0], d->k_stride[1], d->k_stride[2], d->Hkv, d->Nk, scratch, chunks);
-    sage3::colmean_finalize_kernel<T, D><<<BH, D, 0, st>>>(scratch, chunks, 1.0f / (float)d->Nk, static_cast<T*>(km));
+    sage3::colmean_finalize_kernel<T, D><<<BH, D, 0, st>>>(scratch, chunks, 1.0f / (float)d->Nk, static_cast<T*>(km), nullptr, d->Hkv, 0);
     return cudaGetLastError();
 }
 

@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
     lib = _cabi.lib()
     for name in declared:
         assert getattr(lib, name) is not None
-    assert lib.sage3_version() == _cabi.ABI_VERSION == 3
+    assert lib.sage3_version() == _cabi.ABI_VERSION == 4
 
 
 def test_strerror_is_total():

@@ -200,6 +200,40 @@ def test_varlen_matches_per_sequence_calls(cuda_device):
         assert O.cosine(out[a:b].cpu(), ref[0]) >= COS_MIN
 
 
+@pytest.mark.parametrize("D,dtype,causal,pbm,give_max", [(128, torch.float16, True, True, False),
+                                                         (64, torch.bfloat16, False, False, True),
+                                                         (128, torch.bfloat16, True, True, True)])
+def test_varlen_batch_is_one_launch_per_kernel_and_exact(cuda_device, D, dtype, causal, pbm, give_max):
+    """The batched variable-length entry (one launch per kernel, lengths read on the device) gives every sequence
+    bit for bit what a call on that sequence alone gives: ragged lengths, a sequence without keys (zeros), one without
+    queries, GQA, causal masks aligned on each sequence's own lengths, both Q smoothing modes."""
+    lens_q = [130, 5, 0, 300, 128, 64]
+    lens_k = [257, 0, 40, 300, 640, 64] if not causal else [257, 0, 40, 300, 640, 100]
+    cq = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32)
+    ck = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)), dtype=torch.int32)
+    g = torch.Generator().manual_seed(33 + D)
+    q = torch.randn(int(cq[-1]), 4, D, generator=g).to(dtype).to(cuda_device)
+    k = (torch.randn(int(ck[-1]), 2, D, generator=g) + 1.5).to(dtype).to(cuda_device)
+    v = torch.randn(int(ck[-1]), 2, D, generator=g).to(dtype).to(cuda_device)
+    if give_max:       # device cu_seqlens + maxima: nothing is read back by the host
+        out = sageattn_varlen(q, k, v, cq.to(cuda_device), ck.to(cuda_device), max(lens_q), max(lens_k), is_causal=causal,
+                              per_block_mean=pbm)
+    else:              # python lists, maxima derived on the host
+        out = sageattn_varlen(q, k, v, cq.tolist(), ck.tolist(), is_causal=causal, per_block_mean=pbm)
+    torch.cuda.synchronize()
+    assert out.shape == q.shape and not torch.isnan(out.float()).any()
+    for i in range(len(lens_q)):
+        a, b, c, d = int(cq[i]), int(cq[i + 1]), int(ck[i]), int(ck[i + 1])
+        if b == a:
+            continue
+        if d == c:
+            assert torch.count_nonzero(out[a:b]) == 0
+            continue
+        one = sageattn3(q[a:b].unsqueeze(0), k[c:d].unsqueeze(0), v[c:d].unsqueeze(0), tensor_layout="NHD", is_causal=causal,
+                        per_block_mean=pbm)
+        assert torch.equal(out[a:b], one[0]), f"sequence {i}"
+
+
 def test_cuda_graph_capture_and_replay(cuda_device):
     """The whole call is a fixed sequence of launches on the caller's stream (no allocation, no synchronization), so it
     can be captured once and replayed: the replay on new input values equals the eager call."""
