@@ -95,3 +95,21 @@ def test_python_surface_rejects_cpu_tensors():
         sageattn3(q, q, q, attn_mask=torch.ones(1))
     with pytest.raises(RuntimeError):
         sageattn3(q, q, q, return_lse=True)
+
+
+def test_varlen_entry_validates_before_touching_the_device():
+    """sage3_fwd_varlen: null and misaligned arguments are refused with codes; the Python wrapper refuses host tensors
+    and badly shaped cu_seqlens."""
+    import torch
+    from sageattention_b200 import sageattn_varlen
+    lib = _cabi.lib()
+    d = _desc(B=3)
+    assert lib.sage3_fwd_varlen(C.byref(d), None, None, None, None, None, None, None, None) == -1
+    assert lib.sage3_fwd_varlen(C.byref(d), 4, 4, 16, 16, 16, 16, None, None) == -1             # no workspace
+    assert lib.sage3_fwd_varlen(C.byref(d), 2, 4, 16, 16, 16, 16, 256, None) == -5   # SAGE3_E_ALIGN: cu_seqlens_q not 4-byte aligned
+    assert lib.sage3_fwd_varlen(C.byref(d), 4, 4, 8, 16, 16, 16, 256, None) == -5    # SAGE3_E_ALIGN: q not 16-byte aligned
+    q = torch.zeros(10, 2, 64, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        sageattn_varlen(q, q, q, [0, 10], [0, 10])
+    with pytest.raises(ValueError):
+        sageattn_varlen(q.unsqueeze(0), q, q, [0, 10], [0, 10])
