@@ -499,11 +499,11 @@ def main():
     att_tops = flops / (att_ms * 1e-3) / 1e12
     fp4_peak = 4.0 * peaks["bf16_sustained"]          # dense FP4 is 4x dense bf16 on this part
     # DRAM traffic of one attention launch: a constant taken from one stored ncu capture of the small profiling case
-    # (16 heads x 16384 tokens, D = 128: 159.6 MB = dram__bytes_read.sum + dram__bytes_write.sum), scaled by B*H*N; the
+    # (16 heads x 16384 tokens, D = 128: 160.6 MB = dram__bytes_read.sum + dram__bytes_write.sum), scaled by B*H*N; the
     # kernel reads each head's operands once from DRAM and writes its output once, so its traffic grows in that proportion.
     traffic, traffic_src = None, None
     if D == 128 and not w["causal"]:
-        traffic = 159.6e6 * (B * Hq * Nq) / (16 * 16384.0)
+        traffic = 160.6e6 * (B * Hq * Nq) / (16 * 16384.0)
         traffic_src = "constant from a stored ncu capture of a smaller case (not measured in this run), scaled in proportion to B*H*N"
     line = dict(
         metric="attention TOPS (4*B*H*Nq*Nk*D/t) of the smooth+NVFP4-quantize+attend path", value=world * flops / (ms_per_step * 1e-3) / 1e12,
