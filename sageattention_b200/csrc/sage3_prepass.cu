@@ -30,6 +30,21 @@ template <> struct Num<__nv_bfloat16> {
         const __nv_bfloat162 pr = __floats2bfloat162_rn(lo, hi);
         return *reinterpret_cast<const uint32_t*>(&pr);
     }
+    // packed pairs: each result rounded once to T, which for sums and differences of two T values equals fp32
+    // arithmetic followed by a rounding to T (the fp32 result is exact unless the smaller operand lies below a
+    // quarter ulp of the larger, where both roundings return the larger operand)
+    static __device__ __forceinline__ uint32_t sub2(uint32_t a, uint32_t b) {
+        const __nv_bfloat162 r = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+        return *reinterpret_cast<const uint32_t*>(&r);
+    }
+    static __device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b) {
+        const __nv_bfloat162 r = __hadd2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+        return *reinterpret_cast<const uint32_t*>(&r);
+    }
+    static __device__ __forceinline__ uint32_t absmax2(uint32_t m, uint32_t a) {   // max(m, |a|) per half
+        const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&m), __habs2(*reinterpret_cast<const __nv_bfloat162*>(&a)));
+        return *reinterpret_cast<const uint32_t*>(&r);
+    }
 };
 template <> struct Num<__half> {
     using T2 = __half2;
@@ -42,6 +57,18 @@ template <> struct Num<__half> {
     static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
         const __half2 pr = __floats2half2_rn(lo, hi);
         return *reinterpret_cast<const uint32_t*>(&pr);
+    }
+    static __device__ __forceinline__ uint32_t sub2(uint32_t a, uint32_t b) {
+        const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+        return *reinterpret_cast<const uint32_t*>(&r);
+    }
+    static __device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b) {
+        const __half2 r = __hadd2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+        return *reinterpret_cast<const uint32_t*>(&r);
+    }
+    static __device__ __forceinline__ uint32_t absmax2(uint32_t m, uint32_t a) {
+        const __half2 r = __hmax2(*reinterpret_cast<const __half2*>(&m), __habs2(*reinterpret_cast<const __half2*>(&a)));
+        return *reinterpret_cast<const uint32_t*>(&r);
     }
 };
 
@@ -102,17 +129,38 @@ __device__ __forceinline__ void unpack16(const uint4& a, const uint4& b, float* 
     }
 }
 
-// One NVFP4 microblock: 16 fp32 values (already on the input type's grid) -> 8 bytes of codes + scale byte.
-__device__ __forceinline__ void quant16(const float* x, uint32_t& lo, uint32_t& hi, uint32_t& sf_byte) {
-    float amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
+// One NVFP4 microblock: 16 fp32 values (already on the input type's grid) and their maximum magnitude -> 8 bytes of
+// codes + scale byte.
+__device__ __forceinline__ void quant16_amax(const float* x, float amax, uint32_t& lo, uint32_t& hi, uint32_t& sf_byte) {
     sf_byte = cvt_e4m3x2(__fdiv_rn(amax, 6.0f), 0.f) & 0xffu;
     const float sf = e4m3_to_float(sf_byte);
     const float inv = (sf == 0.f) ? 0.f : __frcp_rn(sf);
     float y[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) y[i] = __fmul_rn(x[i], inv);
+    lo = cvt_e2m1x8(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7]);
+    hi = cvt_e2m1x8(y[8], y[9], y[10], y[11], y[12], y[13], y[14], y[15]);
+}
+
+// The same from eight packed words of the input type (16 values): the maximum magnitude is found on the packed pairs
+// (exact, as fp4_quantization_4d.cu:186-196 does), the scaling runs in fp32.
+template <typename T>
+__device__ __forceinline__ void quant16_packed(const uint32_t* w, uint32_t& lo, uint32_t& hi, uint32_t& sf_byte) {
+    uint32_t m = Num<T>::absmax2(0u, w[0]);
+#pragma unroll
+    for (int i = 1; i < 8; ++i) m = Num<T>::absmax2(m, w[i]);
+    const float2 mm = Num<T>::to_f2(m);
+    const float amax = fmaxf(mm.x, mm.y);
+    sf_byte = cvt_e4m3x2(__fdiv_rn(amax, 6.0f), 0.f) & 0xffu;
+    const float sf = e4m3_to_float(sf_byte);
+    const float inv = (sf == 0.f) ? 0.f : __frcp_rn(sf);
+    float y[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float2 v = Num<T>::to_f2(w[i]);
+        y[2 * i] = __fmul_rn(v.x, inv);
+        y[2 * i + 1] = __fmul_rn(v.y, inv);
+    }
     lo = cvt_e2m1x8(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7]);
     hi = cvt_e2m1x8(y[8], y[9], y[10], y[11], y[12], y[13], y[14], y[15]);
 }
@@ -252,22 +300,14 @@ __global__ void __launch_bounds__(256, 3) quant_rows_kernel(
         __syncthreads();
         {
             const int chain = t / (D / 4), c4 = (t % (D / 4)) * 4;
-            auto add_t = [](float a, float b) { return Num<T>::to_f(Num<T>::from_f(a + b)); };
-            float acc[4];
-            {
-                const uint2 w0 = *reinterpret_cast<const uint2*>(s_tile + chain * D + c4);
-                const float2 lo = Num<T>::to_f2(w0.x), hi = Num<T>::to_f2(w0.y);
-                acc[0] = lo.x; acc[1] = lo.y; acc[2] = hi.x; acc[3] = hi.y;
-            }
+            uint2 acc = *reinterpret_cast<const uint2*>(s_tile + chain * D + c4);
 #pragma unroll
             for (int rep = 1; rep < REPS; ++rep) {
                 const uint2 w1 = *reinterpret_cast<const uint2*>(s_tile + (rep * R + chain) * D + c4);
-                const float2 lo = Num<T>::to_f2(w1.x), hi = Num<T>::to_f2(w1.y);
-                acc[0] = add_t(acc[0], lo.x); acc[1] = add_t(acc[1], lo.y);
-                acc[2] = add_t(acc[2], hi.x); acc[3] = add_t(acc[3], hi.y);
+                acc.x = Num<T>::add2(acc.x, w1.x);
+                acc.y = Num<T>::add2(acc.y, w1.y);
             }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) s_part[chain * D + c4 + j] = Num<T>::from_f(acc[j]);
+            *reinterpret_cast<uint2*>(s_part + chain * D + c4) = acc;
         }
         __syncthreads();
         if (t < D) {
@@ -300,21 +340,21 @@ __global__ void __launch_bounds__(256, 3) quant_rows_kernel(
     }
     __syncthreads();
 
-    float mu[16];
+    uint32_t mu2[8];       // the 16 means of this thread's columns, packed (they are values of the input type)
 #pragma unroll
-    for (int j = 0; j < 16; ++j) mu[j] = s_mean[c * 16 + j];
+    for (int j = 0; j < 8; ++j) mu2[j] = Num<T>::pack2(s_mean[c * 16 + 2 * j], s_mean[c * 16 + 2 * j + 1]);
 
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
         const int rt = rl + RPP * i;          // row inside the tile
         const int r = row0 + rt;
-        float y[16];
-        unpack16<T>(raw[i][0], raw[i][1], y);
         // rows beyond N hold 0 - mean (Q is padded before smoothing); they are never read back
+        const uint32_t x2[8] = {raw[i][0].x, raw[i][0].y, raw[i][0].z, raw[i][0].w, raw[i][1].x, raw[i][1].y, raw[i][1].z, raw[i][1].w};
+        uint32_t d2[8];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) y[j] = Num<T>::to_f(Num<T>::from_f(y[j] - mu[j]));
+        for (int j = 0; j < 8; ++j) d2[j] = Num<T>::sub2(x2[j], mu2[j]);
         uint32_t lo, hi, sfb;
-        quant16(y, lo, hi, sfb);
+        quant16_packed<T>(d2, lo, hi, sfb);
         *reinterpret_cast<uint2*>(codes + ((int64_t)bh * Np + r) * (D / 2) + c * 8) = make_uint2(lo, hi);
         s_sf[sf_atom_offset(rt, c)] = static_cast<uint8_t>(sfb);
     }
@@ -389,31 +429,23 @@ __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    float mu[16];
+    uint32_t mu2[8];       // the 16 means of this thread's columns, packed (they are values of the input type)
 #pragma unroll
-    for (int j = 0; j < 16; ++j) mu[j] = s_mean[c * 16 + j];
+    for (int j = 0; j < 8; ++j) mu2[j] = Num<T>::pack2(s_mean[c * 16 + 2 * j], s_mean[c * 16 + 2 * j + 1]);
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
         const int rt = rl + RPP * i;          // row inside the tile
         const int r = row0 + rt;
-        float y[16];
-        unpack16<T>(raw[i][0], raw[i][1], y);
         const bool zero_row = (r >= N);       // K is padded after smoothing: pad rows are 0
+        const uint32_t x2[8] = {raw[i][0].x, raw[i][0].y, raw[i][0].z, raw[i][0].w, raw[i][1].x, raw[i][1].y, raw[i][1].z, raw[i][1].w};
+        uint32_t w[8];         // k' of this item, packed: quantized below and stored as the MMA operand as it is
 #pragma unroll
-        for (int j = 0; j < 16; ++j) y[j] = zero_row ? 0.f : Num<T>::to_f(Num<T>::from_f(y[j] - mu[j]));
+        for (int j = 0; j < 8; ++j) w[j] = zero_row ? 0u : Num<T>::sub2(x2[j], mu2[j]);
         uint32_t lo, hi, sfb;
-        quant16(y, lo, hi, sfb);
+        quant16_packed<T>(w, lo, hi, sfb);
         *reinterpret_cast<uint2*>(codes + ((int64_t)bh * Np + r) * (D / 2) + c * 8) = make_uint2(lo, hi);
         s_sf[sf_atom_offset(rt, c)] = static_cast<uint8_t>(sfb);
         // k' into the B tile: this item's 16 elements are the 16-byte chunks 2c, 2c+1 of row rt
-        uint32_t w[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            typename Num<T>::T2 pr;
-            pr.x = Num<T>::from_f(y[2 * j]);
-            pr.y = Num<T>::from_f(y[2 * j + 1]);
-            w[j] = *reinterpret_cast<uint32_t*>(&pr);
-        }
 #pragma unroll
         for (int q2 = 0; q2 < 2; ++q2) {
             const int chunk = 2 * c + q2, sub = chunk >> 3, cw = chunk & 7;
@@ -562,17 +594,21 @@ __global__ void __launch_bounds__(256) quant_vt_kernel(const __grid_constant__ S
     for (int item = t; item < (D / 2) * 8; item += 256) {
         const int dp = item % (D / 2), mb = item / (D / 2);
         float y0[16], y1[16];
+        uint32_t m2 = 0u;           // running maximum magnitude of both channels, packed
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-            const float2 v2 = Num<T>::to_f2(*reinterpret_cast<const uint32_t*>(s_v + (mb * 16 + i) * PITCH + 2 * dp));
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(s_v + (mb * 16 + i) * PITCH + 2 * dp);
+            m2 = Num<T>::absmax2(m2, w);
+            const float2 v2 = Num<T>::to_f2(w);
             y0[i] = v2.x;
             y1[i] = v2.y;
         }
+        const float2 amax2 = Num<T>::to_f2(m2);
         uint32_t lo, hi, sfb;
-        quant16(y0, lo, hi, sfb);
+        quant16_amax(y0, amax2.x, lo, hi, sfb);
         *reinterpret_cast<uint2*>(s_out + (2 * dp) * OPITCH + mb * 8) = make_uint2(lo, hi);
         s_sf[sf_atom_offset(2 * dp, mb)] = static_cast<uint8_t>(sfb);
-        quant16(y1, lo, hi, sfb);
+        quant16_amax(y1, amax2.y, lo, hi, sfb);
         *reinterpret_cast<uint2*>(s_out + (2 * dp + 1) * OPITCH + mb * 8) = make_uint2(lo, hi);
         s_sf[sf_atom_offset(2 * dp + 1, mb)] = static_cast<uint8_t>(sfb);
     }
