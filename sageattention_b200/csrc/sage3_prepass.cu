@@ -226,7 +226,7 @@ __global__ void colmean_finalize_kernel(const float* __restrict__ part, int chun
 enum { kModeQBlockMean = 0, kModeQGlobalMean = 1 };
 
 template <typename T, int D, int MODE>
-__global__ void __launch_bounds__(256, 3) quant_rows_kernel(
+__global__ void __launch_bounds__(256, D == 128 ? 4 : 3) quant_rows_kernel(
     const __grid_constant__ Src<T> x, int64_t sb, int64_t sh, int64_t sn, int H, int N, int Np,
     const T* __restrict__ mean_in,     // one mean per head: qm [B*H][D]; unused for block mean
     T* __restrict__ qm_out,            // block mean: [B*H][Np/128][D]
@@ -560,7 +560,7 @@ __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
 // V: one tile of 128 tokens x D channels per CTA -> V^T codes (microblocks along tokens) + scale atoms
 // ------------------------------------------------------------------------------------------------
 template <typename T, int D>
-__global__ void __launch_bounds__(256) quant_vt_kernel(const __grid_constant__ Src<T> x, int64_t sb, int64_t sh, int64_t sn,
+__global__ void __launch_bounds__(256, 5) quant_vt_kernel(const __grid_constant__ Src<T> x, int64_t sb, int64_t sh, int64_t sn,
                                                        int H, int N, int Np, uint8_t* __restrict__ codes,
                                                        uint8_t* __restrict__ sfs) {
     constexpr int PITCH = D + 2;          // elements; word pitch odd -> column reads are conflict-free
