@@ -65,3 +65,33 @@ def test_prepass_matches_oracle(cuda_device, B, Hq, Hkv, Nq, Nk, D, dt, pbm, lay
     bad = (d_dev - d_ref).abs() > tol + eps * d_ref.abs()
     assert bad.float().mean() < 1e-3, f"delta_s mismatch fraction {bad.float().mean():.2e}"
     assert (d_dev - d_ref).abs().max() <= 4 * eps * d_ref.abs().max() + 1e-6
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("pbm", [True, False])
+def test_packed_16bit_arithmetic_equals_fp32_then_round(cuda_device, dt, pbm):
+    """The kernels subtract the means, add the chain sums of the block mean and take the microblock maxima on packed
+    16-bit pairs (one rounding to the input type per operation); the oracle computes in fp32 and rounds.  The two must
+    agree bit for bit also where operands differ by many binades: channels scaled from 2^-12 to 2^6, means far larger or
+    far smaller than the values they are subtracted from, exact cancellations."""
+    B, H, N, D = 1, 2, 512, 128
+    g = torch.Generator().manual_seed(77)
+    scale = torch.pow(2.0, torch.randint(-12, 7, (1, H, 1, D), generator=g).float())
+    q = (torch.randn(B, H, N, D, generator=g) * scale + torch.randn(1, H, 1, D, generator=g) * scale.flip(-1)).to(dt)
+    k = (torch.randn(B, H, N, D, generator=g) * scale.flip(-1) + 3 * torch.randn(1, H, 1, D, generator=g) * scale).to(dt)
+    k[:, :, :, 5] = k[:, :, :1, 5]                       # a constant channel: k - mean cancels exactly
+    q[:, :, 128:256, 9] = q[:, :, 128:129, 9]            # a constant channel inside one 128-row block
+    v = (torch.randn(B, H, N, D, generator=g) * scale).to(dt)
+    prob = Sage3Problem(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), per_block_mean=pbm)
+    prob.prepass()
+    torch.cuda.synchronize()
+    assert prob.check_status() == 0
+    ws = read_workspace(prob)
+    ref0 = O.prepass(q, k, v, per_block_mean=pbm)
+    if pbm:
+        assert torch.equal(ws["qm"], ref0.qm), "Q block mean (16-bit chain sums)"
+    ref = O.prepass(q, k, v, per_block_mean=pbm, km_override=ws["km"], qm_override=ws["qm"])
+    for name in ("q_sf", "k_sf", "vt_sf"):
+        assert torch.equal(ws[name], getattr(ref, name)), name
+    for name in ("q_codes", "k_codes", "vt_codes"):
+        assert torch.equal(canon(ws[name]), canon(getattr(ref, name))), name
