@@ -328,6 +328,8 @@ def sageattn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlen
     if isinstance(sm_scale, torch.Tensor):
         raise ValueError("sageattn_varlen takes a scalar sm_scale")
     kwargs.pop("smooth_k", None)
+    if kwargs.get("return_lse"):
+        raise NotImplementedError("sageattn_varlen has no LSE output (call sageattn3 per sequence for it)")
     dev = q.device
     Hq, Hkv, D = q.shape[1], k.shape[1], q.shape[2]
     if D not in (64, 128):
