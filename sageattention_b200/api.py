@@ -343,6 +343,18 @@ def sageattn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlen
     cq, ck = as_cu(cu_seqlens_q), as_cu(cu_seqlens_k)
     if cq.dim() != 1 or cq.shape != ck.shape or cq.numel() < 2:
         raise ValueError("cu_seqlens_q / cu_seqlens_k must be 1-D, of equal length >= 2")
+    if torch.compiler.is_compiling():
+        # one opaque operator under torch.compile (the maxima must be given: reading them back would break the graph)
+        if max_seqlen_q is None or max_seqlen_k is None:
+            raise ValueError("under torch.compile sageattn_varlen needs max_seqlen_q and max_seqlen_k")
+        return torch.ops.sageattention_b200.fwd_varlen(q, k, v, cq, ck, int(max_seqlen_q), int(max_seqlen_k), bool(is_causal),
+                                                       None if sm_scale is None else float(sm_scale), bool(per_block_mean))
+    return _varlen_impl(q, k, v, cq, ck, max_seqlen_q, max_seqlen_k, is_causal, sm_scale, per_block_mean)
+
+
+def _varlen_impl(q, k, v, cq, ck, max_seqlen_q, max_seqlen_k, is_causal, sm_scale, per_block_mean):
+    dev = q.device
+    Hq, Hkv, D = q.shape[1], k.shape[1], q.shape[2]
     nseq = cq.numel() - 1
     if max_seqlen_q is None or max_seqlen_k is None:
         # the one place that looks at the lengths on the host (and checks them while it is at it)
@@ -385,6 +397,18 @@ def sageattn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlen
                                                  vc.data_ptr(), out.data_ptr(), buf.data_ptr() + shift,
                                                  torch.cuda.current_stream(dev).cuda_stream), "sage3_fwd_varlen")
     return out
+
+
+@torch.library.custom_op("sageattention_b200::fwd_varlen", mutates_args=(), device_types="cuda")
+def _fwd_varlen_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q: torch.Tensor, cu_seqlens_k: torch.Tensor,
+                   max_seqlen_q: int, max_seqlen_k: int, is_causal: bool, sm_scale: float | None,
+                   per_block_mean: bool) -> torch.Tensor:
+    return _varlen_impl(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, is_causal, sm_scale, per_block_mean)
+
+
+@_fwd_varlen_op.register_fake
+def _(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, is_causal, sm_scale, per_block_mean):
+    return torch.empty(q.shape, dtype=q.dtype, device=q.device)
 
 
 _OFFLOAD_STATE: dict = {}

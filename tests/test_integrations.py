@@ -140,6 +140,11 @@ def test_custom_op_traces_with_fake_tensors():
         assert o.shape == q.shape and o.dtype == q.dtype
         o, lse = torch.ops.sageattention_b200.fwd_lse(q.transpose(1, 2), k.transpose(1, 2), k.transpose(1, 2), "NHD", True, 0.1, None, True)
         assert o.shape == (2, 300, 8, 64) and lse.shape == (2, 8, 300) and lse.dtype == torch.float32
+        qp = torch.empty(100, 4, 64, dtype=torch.bfloat16, device="cuda")
+        kp = torch.empty(120, 2, 64, dtype=torch.bfloat16, device="cuda")
+        cu = torch.empty(3, dtype=torch.int32, device="cuda")
+        o = torch.ops.sageattention_b200.fwd_varlen(qp, kp, kp, cu, cu, 60, 70, True, None, True)
+        assert o.shape == qp.shape and o.dtype == qp.dtype
 
 
 # ------------------------------------------------------------------------------------------------------ GPU
@@ -186,3 +191,24 @@ def test_torch_compile_fullgraph(cuda_device):
     torch.cuda.synchronize()
     assert torch.allclose(eager.float(), comp.float(), atol=2e-2, rtol=2e-2)
     assert torch.allclose(lse_e, lse_c, atol=1e-3)
+
+
+@pytest.mark.gpu
+def test_torch_compile_varlen_fullgraph(cuda_device):
+    """sageattn_varlen inside a compiled function: one opaque operator (cu_seqlens on the device, maxima given)."""
+    from sageattention_b200 import sageattn_varlen
+    g = torch.Generator().manual_seed(8)
+    lens = [70, 200, 33]
+    cu = torch.tensor([0, 70, 270, 303], dtype=torch.int32, device=cuda_device)
+    q = torch.randn(303, 4, 64, generator=g).to(torch.bfloat16).to(cuda_device)
+    k = (torch.randn(303, 2, 64, generator=g) + 1).to(torch.bfloat16).to(cuda_device)
+    v = torch.randn(303, 2, 64, generator=g).to(torch.bfloat16).to(cuda_device)
+
+    def fn(q, k, v, cu):
+        return sageattn_varlen(q * 1.0, k, v, cu, cu, max(lens), max(lens), is_causal=True) + 0.0
+
+    with torch.no_grad():
+        eager = fn(q, k, v, cu)
+        comp = torch.compile(fn, fullgraph=True, backend="aot_eager")(q, k, v, cu)
+    torch.cuda.synchronize()
+    assert torch.equal(eager, comp)
