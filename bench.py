@@ -47,6 +47,10 @@ WORKLOADS = {
                          inp=dict(rope_base=500000.0)),
     "ncu_small": dict(B=1, Hq=16, Hkv=16, Nq=16384, Nk=16384, D=128, causal=False, layout="HND",
                       inp=dict(k_offset_std=3.0)),
+    "ncu_small_hd64": dict(B=1, Hq=32, Hkv=32, Nq=16384, Nk=16384, D=64, causal=False, layout="HND",
+                           inp=dict(k_offset_std=3.0)),
+    "ncu_small_causal": dict(B=1, Hq=32, Hkv=8, Nq=8192, Nk=8192, D=128, causal=True, layout="NHD",
+                             inp=dict(rope_base=500000.0)),
     "c1_small": dict(B=1, Hq=2, Hkv=2, Nq=1024, Nk=1024, D=128, causal=False, layout="HND",
                      inp=dict(k_offset_std=3.0)),
 }
