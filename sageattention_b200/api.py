@@ -364,11 +364,11 @@ def _varlen_impl(q, k, v, cq, ck, max_seqlen_q, max_seqlen_k, is_causal, sm_scal
             raise ValueError("cu_seqlens_q / cu_seqlens_k must start at 0, be non-decreasing and end at the token counts")
         max_seqlen_q = max(b - a for a, b in zip(hq, hq[1:]))
         max_seqlen_k = max(b - a for a, b in zip(hk, hk[1:]))
-    out = torch.empty_like(q if _usable(q) else q.contiguous())
+    qc, kc, vc = (t if _usable(t) else t.contiguous() for t in (q, k, v))
+    out = torch.empty_like(qc)
     if q.shape[0] == 0:
         return out
     max_seqlen_q, max_seqlen_k = max(int(max_seqlen_q), 1), max(int(max_seqlen_k), 1)
-    qc, kc, vc = (t if _usable(t) else t.contiguous() for t in (q, k, v))
     d = _cabi.Sage3Desc()
     d.B, d.Hq, d.Hkv, d.Nq, d.Nk, d.D = nseq, Hq, Hkv, max_seqlen_q, max_seqlen_k, D
     d.dtype = _DTYPES[q.dtype]
