@@ -134,10 +134,12 @@ SAGE3_API int sage3_attn_fwd(const Sage3Desc* desc, void* ws, void* out, float* 
  * stride[1] = head stride, stride[2] = token stride, stride[0] unused.  Every sequence is smoothed, quantized and
  * attended exactly as a sage3_fwd call on it alone would be (its own K mean, its own padding to 128 rows, causal mask
  * aligned on its own lengths); a sequence without keys gets zeros.  The workspace is the one of a uniform batch of B
- * entries of the maximum lengths (sage3_workspace_bytes(desc)).  No LSE output, no per-call K mean, no carried state.
+ * entries of the maximum lengths (sage3_workspace_bytes(desc)).  `lse`: NULL, or fp32 [B][Hq][desc->Nq] that receives the
+ * log-sum-exp of every query row of sequence b at [b][h][0 .. len_q(b)) (entries beyond a sequence's length are not
+ * written).  No per-call K mean, no carried state.
  */
 SAGE3_API int sage3_fwd_varlen(const Sage3Desc* desc, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, const void* q,
-                               const void* k, const void* v, void* out, void* ws, void* stream);
+                               const void* k, const void* v, void* out, float* lse, void* ws, void* stream);
 
 /*
  * sage3_prepass with the K mean supplied by the caller: `km` is a device array dtype[B][Hkv][D] that is used instead of

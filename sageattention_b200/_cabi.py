@@ -99,7 +99,7 @@ def lib() -> C.CDLL:
     l.sage3_fwd.restype = C.c_int
     l.sage3_fwd.argtypes = [P(Sage3Desc), V, V, V, V, V, V, V]
     l.sage3_fwd_varlen.restype = C.c_int
-    l.sage3_fwd_varlen.argtypes = [P(Sage3Desc), V, V, V, V, V, V, V, V]
+    l.sage3_fwd_varlen.argtypes = [P(Sage3Desc), V, V, V, V, V, V, V, V, V]
     l.sage3_selftest_wait_timeout.restype = C.c_int
     l.sage3_selftest_wait_timeout.argtypes = [V, V]
     l.sage3_slab_copy.restype = C.c_int

@@ -305,7 +305,7 @@ def sageattn(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, retur
 
 def sageattn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q, cu_seqlens_k,
                     max_seqlen_q: int | None = None, max_seqlen_k: int | None = None, is_causal: bool = False,
-                    sm_scale=None, per_block_mean: bool = True, **kwargs) -> torch.Tensor:
+                    sm_scale=None, per_block_mean: bool = True, return_lse: bool = False, **kwargs):
     """Signature of the reference's packed variable-length entry (sageattention/core.py:334-345): q
     [total_q, Hq, D], k, v [total_k, Hkv, D]; sequence i owns rows cu_seqlens[i]:cu_seqlens[i+1].  Returns
     [total_q, Hq, D].
@@ -315,7 +315,8 @@ def sageattn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlen
     gets zeros.  With `max_seqlen_q` / `max_seqlen_k` given and cu_seqlens already int32 CUDA tensors the call does not
     synchronize with the device; without them the maxima are read from cu_seqlens (one device-to-host copy).  Scratch is
     sized for `number of sequences x maximum lengths`.  `smooth_k` is accepted for compatibility; a scalar `sm_scale`
-    only."""
+    only.  With `return_lse=True` the result is `(out, lse)`, lse fp32 [number of sequences, Hq, max_seqlen_q]: row i of
+    sequence b at [b, :, i], -inf beyond a sequence's length (natural log, as `sageattn3(..., return_lse=True)`)."""
     if q.dim() != 3 or k.dim() != 3 or v.dim() != 3:
         raise ValueError("q, k, v must be packed as [tokens, heads, head_dim]")
     for name, t in (("q", q), ("k", k), ("v", v)):
@@ -328,8 +329,6 @@ def sageattn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlen
     if isinstance(sm_scale, torch.Tensor):
         raise ValueError("sageattn_varlen takes a scalar sm_scale")
     kwargs.pop("smooth_k", None)
-    if kwargs.get("return_lse"):
-        raise NotImplementedError("sageattn_varlen has no LSE output (call sageattn3 per sequence for it)")
     dev = q.device
     Hq, Hkv, D = q.shape[1], k.shape[1], q.shape[2]
     if D not in (64, 128):
@@ -347,12 +346,14 @@ def sageattn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlen
         # one opaque operator under torch.compile (the maxima must be given: reading them back would break the graph)
         if max_seqlen_q is None or max_seqlen_k is None:
             raise ValueError("under torch.compile sageattn_varlen needs max_seqlen_q and max_seqlen_k")
+        if return_lse:
+            raise NotImplementedError("return_lse of sageattn_varlen is not registered for torch.compile")
         return torch.ops.sageattention_b200.fwd_varlen(q, k, v, cq, ck, int(max_seqlen_q), int(max_seqlen_k), bool(is_causal),
                                                        None if sm_scale is None else float(sm_scale), bool(per_block_mean))
-    return _varlen_impl(q, k, v, cq, ck, max_seqlen_q, max_seqlen_k, is_causal, sm_scale, per_block_mean)
+    return _varlen_impl(q, k, v, cq, ck, max_seqlen_q, max_seqlen_k, is_causal, sm_scale, per_block_mean, return_lse)
 
 
-def _varlen_impl(q, k, v, cq, ck, max_seqlen_q, max_seqlen_k, is_causal, sm_scale, per_block_mean):
+def _varlen_impl(q, k, v, cq, ck, max_seqlen_q, max_seqlen_k, is_causal, sm_scale, per_block_mean, return_lse=False):
     dev = q.device
     Hq, Hkv, D = q.shape[1], k.shape[1], q.shape[2]
     nseq = cq.numel() - 1
@@ -366,9 +367,10 @@ def _varlen_impl(q, k, v, cq, ck, max_seqlen_q, max_seqlen_k, is_causal, sm_scal
         max_seqlen_k = max(b - a for a, b in zip(hk, hk[1:]))
     qc, kc, vc = (t if _usable(t) else t.contiguous() for t in (q, k, v))
     out = torch.empty_like(qc)
-    if q.shape[0] == 0:
-        return out
     max_seqlen_q, max_seqlen_k = max(int(max_seqlen_q), 1), max(int(max_seqlen_k), 1)
+    lse = torch.full((nseq, Hq, max_seqlen_q), float("-inf"), dtype=torch.float32, device=dev) if return_lse else None
+    if q.shape[0] == 0:
+        return (out, lse) if return_lse else out
     d = _cabi.Sage3Desc()
     d.B, d.Hq, d.Hkv, d.Nq, d.Nk, d.D = nseq, Hq, Hkv, max_seqlen_q, max_seqlen_k, D
     d.dtype = _DTYPES[q.dtype]
@@ -394,9 +396,10 @@ def _varlen_impl(q, k, v, cq, ck, max_seqlen_q, max_seqlen_k, is_causal, sm_scal
     shift = (-buf.data_ptr()) % 256
     with torch.cuda.device(dev):
         _cabi.check(_cabi.lib().sage3_fwd_varlen(C.byref(d), cq.data_ptr(), ck.data_ptr(), qc.data_ptr(), kc.data_ptr(),
-                                                 vc.data_ptr(), out.data_ptr(), buf.data_ptr() + shift,
-                                                 torch.cuda.current_stream(dev).cuda_stream), "sage3_fwd_varlen")
-    return out
+                                                 vc.data_ptr(), out.data_ptr(), lse.data_ptr() if lse is not None else None,
+                                                 buf.data_ptr() + shift, torch.cuda.current_stream(dev).cuda_stream),
+                    "sage3_fwd_varlen")
+    return (out, lse) if return_lse else out
 
 
 @torch.library.custom_op("sageattention_b200::fwd_varlen", mutates_args=(), device_types="cuda")

@@ -318,12 +318,12 @@ SAGE3_API int sage3_prepass(const Sage3Desc* desc, const void* q, const void* k,
 // cu[b] .. cu[b + 1] of the packed tensors.  One launch of every kernel covers the whole batch; the workspace has the
 // layout of a uniform batch of the maximum lengths, and CTAs beyond a sequence's own length leave at once.
 SAGE3_API int sage3_fwd_varlen(const Sage3Desc* desc, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, const void* q,
-                               const void* k, const void* v, void* out, void* ws, void* stream) {
+                               const void* k, const void* v, void* out, float* lse, void* ws, void* stream) {
     if (!desc || !cu_seqlens_q || !cu_seqlens_k || !q || !k || !v || !out) return SAGE3_E_NULL;
     if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(cu_seqlens_q, 4) || !aligned(cu_seqlens_k, 4)) return SAGE3_E_ALIGN;
     const int rc = prepass_impl(desc, one_part(q), one_part(k), one_part(v), nullptr, ws, stream, cu_seqlens_q, cu_seqlens_k);
     if (rc != SAGE3_OK) return rc;
-    return attn_impl(desc, ws, one_part(out), nullptr, nullptr, stream, nullptr, cu_seqlens_q, cu_seqlens_k);
+    return attn_impl(desc, ws, one_part(out), lse, nullptr, stream, nullptr, cu_seqlens_q, cu_seqlens_k);
 }
 
 SAGE3_API int sage3_prepass_kmean(const Sage3Desc* desc, const void* q, const void* k, const void* v, const void* km, void* ws,

@@ -104,10 +104,10 @@ def test_varlen_entry_validates_before_touching_the_device():
     from sageattention_b200 import sageattn_varlen
     lib = _cabi.lib()
     d = _desc(B=3)
-    assert lib.sage3_fwd_varlen(C.byref(d), None, None, None, None, None, None, None, None) == -1
-    assert lib.sage3_fwd_varlen(C.byref(d), 4, 4, 16, 16, 16, 16, None, None) == -1             # no workspace
-    assert lib.sage3_fwd_varlen(C.byref(d), 2, 4, 16, 16, 16, 16, 256, None) == -5   # SAGE3_E_ALIGN: cu_seqlens_q not 4-byte aligned
-    assert lib.sage3_fwd_varlen(C.byref(d), 4, 4, 8, 16, 16, 16, 256, None) == -5    # SAGE3_E_ALIGN: q not 16-byte aligned
+    assert lib.sage3_fwd_varlen(C.byref(d), None, None, None, None, None, None, None, None, None) == -1
+    assert lib.sage3_fwd_varlen(C.byref(d), 4, 4, 16, 16, 16, 16, None, None, None) == -1             # no workspace
+    assert lib.sage3_fwd_varlen(C.byref(d), 2, 4, 16, 16, 16, 16, None, 256, None) == -5   # SAGE3_E_ALIGN: cu_seqlens_q not 4-byte aligned
+    assert lib.sage3_fwd_varlen(C.byref(d), 4, 4, 8, 16, 16, 16, None, 256, None) == -5    # SAGE3_E_ALIGN: q not 16-byte aligned
     q = torch.zeros(10, 2, 64, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError):
         sageattn_varlen(q, q, q, [0, 10], [0, 10])

@@ -234,6 +234,28 @@ def test_varlen_batch_is_one_launch_per_kernel_and_exact(cuda_device, D, dtype, 
         assert torch.equal(out[a:b], one[0]), f"sequence {i}"
 
 
+def test_varlen_lse_matches_per_sequence_calls(cuda_device):
+    """LSE of a packed batch: [sequence, head, row] equals the per-sequence call's, -inf beyond a sequence's length."""
+    lens_q, lens_k = [130, 5, 300], [257, 40, 300]
+    cq = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32)
+    ck = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)), dtype=torch.int32)
+    g = torch.Generator().manual_seed(91)
+    q = torch.randn(int(cq[-1]), 4, 128, generator=g).to(torch.bfloat16).to(cuda_device)
+    k = (torch.randn(int(ck[-1]), 2, 128, generator=g) + 1.5).to(torch.bfloat16).to(cuda_device)
+    v = torch.randn(int(ck[-1]), 2, 128, generator=g).to(torch.bfloat16).to(cuda_device)
+    out, lse = sageattn_varlen(q, k, v, cq.to(cuda_device), ck.to(cuda_device), max(lens_q), max(lens_k), is_causal=True,
+                               return_lse=True)
+    torch.cuda.synchronize()
+    assert lse.shape == (3, 4, max(lens_q)) and lse.dtype == torch.float32
+    for i in range(3):
+        a, b, c, d = int(cq[i]), int(cq[i + 1]), int(ck[i]), int(ck[i + 1])
+        one, lse1 = sageattn3(q[a:b].unsqueeze(0), k[c:d].unsqueeze(0), v[c:d].unsqueeze(0), tensor_layout="NHD", is_causal=True,
+                              return_lse=True)
+        assert torch.equal(out[a:b], one[0])
+        assert torch.equal(lse[i, :, :b - a], lse1[0])
+        assert bool(torch.isinf(lse[i, :, b - a:]).all())
+
+
 def test_cuda_graph_capture_and_replay(cuda_device):
     """The whole call is a fixed sequence of launches on the caller's stream (no allocation, no synchronization), so it
     can be captured once and replayed: the replay on new input values equals the eager call."""
