@@ -730,6 +730,14 @@ static CUresult make_map(EncodeTiledFn fn, CUtensorMap* m, const void* base, uin
               CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 }
 
+int encode_tiled_bytes(void* map64, const void* base, uint64_t n0, uint64_t n1, uint64_t n2, uint32_t b0, uint32_t b1, int swizzle) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return -1;
+    const CUtensorMapSwizzle swz = swizzle == 3 ? CU_TENSOR_MAP_SWIZZLE_128B : swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                 : swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE;
+    return (int)make_map(fn, static_cast<CUtensorMap*>(map64), base, n0, n1, n2, b0, b1, swz);
+}
+
 template <int D, bool CAUSAL, typename OutT, bool VARLEN>
 static cudaError_t launch_v(const AttnArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                             const AttnParams& p, cudaStream_t st) {

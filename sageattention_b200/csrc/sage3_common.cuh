@@ -16,7 +16,7 @@ constexpr int kMicro = 16;    // NVFP4 microblock
 enum : int {
     kWaitQFull = 101, kWaitKFull = 102, kWaitVFull = 103, kWaitKEmpty = 104, kWaitVEmpty = 105,
     kWaitSFull = 106, kWaitSEmpty = 107, kWaitPFull = 108, kWaitOReady = 109, kWaitPair = 110,
-    kWaitPEmpty = 113, kWaitAlpha = 114, kWaitOScaled = 112, kWaitDeltaMma = 116, kWaitSelfTest = 199
+    kWaitPEmpty = 113, kWaitAlpha = 114, kWaitOScaled = 112, kWaitDeltaMma = 116, kWaitDeltaA = 117, kWaitSelfTest = 199
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -182,6 +182,14 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"(tmap), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
 }
+// shared -> global tile store (bulk group); the issuing thread commits the group and, before the shared-memory tile is
+// written again, waits until the engine has read it
+__device__ __forceinline__ void tma_store_3d(const void* tmap, uint32_t src, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(tmap), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 // contiguous global -> shared copy; src, dst 16-byte aligned, bytes % 16 == 0
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile(

@@ -57,6 +57,10 @@ struct AttnArgs {
 #endif
 };
 
+// Encodes a tensor map over a byte tensor [n2][n1][n0] (n0 contiguous) with box [1][b1][b0]; swizzle: 0 none, 1 32 B, 2 64 B,
+// 3 128 B.  Returns 0, or the driver's error code (-1: the driver entry point could not be resolved).
+int encode_tiled_bytes(void* map64, const void* base, uint64_t n0, uint64_t n1, uint64_t n2, uint32_t b0, uint32_t b1, int swizzle);
+
 cudaError_t launch_prepass(const PrepassArgs& a, cudaStream_t st);
 // returns cudaSuccess, or an error; `driver_rc` receives a CUresult when tensor-map encoding failed
 cudaError_t launch_attn(const AttnArgs& a, cudaStream_t st, int* driver_rc);

@@ -12,6 +12,8 @@
 #include <mutex>
 
 #include "../../include/sage3_b200.h"
+#include <cuda.h>
+
 #include "sage3_common.cuh"
 #include "sage3_kernels.h"
 
@@ -112,11 +114,6 @@ __device__ __forceinline__ void load16_packed(const T* p, bool valid, uint4& a, 
         a = __ldg(reinterpret_cast<const uint4*>(p));
         b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
     }
-}
-// 256-bit store (32-byte aligned address): one whole sector per lane
-__device__ __forceinline__ void st_global_256(void* p, const uint32_t* w) {
-    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                 ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
 }
 template <typename T>
 __device__ __forceinline__ void unpack16(const uint4& a, const uint4& b, float* f) {   // 16 elements -> fp32
@@ -370,6 +367,9 @@ __global__ void __launch_bounds__(256, D == 128 ? 4 : 3) quant_rows_kernel(
 // K: smooth + quantize one 128-key tile per CTA, and its delta_s columns on the tensor core:
 // delta_s[qb][key] = sum_d qm[qb][d] * k'[key][d] as 128 x 128 x D tcgen05 MMAs (16-bit operands from shared
 // memory in the 128-byte-swizzled K-major layout, fp32 accumulator in tensor memory), one per 128 query blocks.
+// The query-block means arrive through TMA (a tensor map over qm) and the delta_s tiles leave through TMA (a tensor
+// map over delta), so the threads' load / store instructions carry only the K rows, the codes and the staging of
+// the converted accumulator.
 // ------------------------------------------------------------------------------------------------
 template <typename T, int D>
 __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
@@ -377,9 +377,9 @@ __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
     const T* __restrict__ km,          // [B*H][D]
     uint8_t* __restrict__ codes,       // [B*H][Np][D/2]
     uint8_t* __restrict__ sfs,         // [B*H][Np/128][D/64][512]
-    const T* __restrict__ qm_all,      // [B][Hq][nqm][D]
-    T* __restrict__ delta,             // [B][Hq][nqm][Np]
-    int Hq, int nqm, int* __restrict__ status, const int* __restrict__ cu_q) {
+    int Hq, int nqm, int* __restrict__ status, const int* __restrict__ cu_q,
+    const __grid_constant__ CUtensorMap tm_qm,       // bytes [B*Hq][nqm][2 D], box 128 rows x 128 bytes, 128-byte swizzle
+    const __grid_constant__ CUtensorMap tm_delta) {  // bytes [B*Hq][nqm][2 Np], box 32 rows x 128 bytes, 128-byte swizzle
     constexpr int CH = D / 16;            // microblocks per row
     constexpr int RPP = 256 / CH;         // rows per pass
     constexpr int ITEMS = kBlock / RPP;   // microblocks per thread
@@ -400,17 +400,21 @@ __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
     extern __shared__ uint8_t smem_dyn[];
     const uint32_t sbase = (smem_u32(smem_dyn) + 1023u) & ~1023u;
     uint8_t* sgen = smem_dyn + (sbase - smem_u32(smem_dyn));
-    // [B tile: k' | A tile: qm chunk] as SUB sub-tiles of 128 rows x 128 bytes each, then small things
+    // [B tile: k' | A tile: qm chunk] as SUB sub-tiles of 128 rows x 128 bytes each, then small things, then (D = 64 only,
+    // where the A tile is too small for it) the staging tile of the epilogue: 8 warps x 32 rows x 128 bytes
     constexpr int oB = 0, oA = SUB * 16384, oMean = 2 * SUB * 16384, oSf = oMean + D * 4, oBar = oSf + SUB * 512;
+    constexpr int oStg = (D == 128) ? oA : ((oBar + 64 + 1023) / 1024) * 1024;
     float* s_mean = reinterpret_cast<float*>(sgen + oMean);
     uint8_t* s_sf = sgen + oSf;
     const uint32_t bar = sbase + oBar;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + oBar + 8);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + oBar + 12);
 
+    const uint32_t bar_a = bar + 16;        // "the A tile has landed" (the bytes between hold the abort flag and the tensor-memory slot)
     if (t == 0) {
         *abort_flag = 0;
         mbar_init(bar, 1);
+        mbar_init(bar_a, 1);
         mbar_fence_init();
     }
     if (warp == 0) {
@@ -467,19 +471,22 @@ __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
     bool alive = true;
     for (int g = 0; g < group && alive; ++g) {
         const int hq = h * group + g;
-        const T* qmh = qm_all + ((int64_t)b * Hq + hq) * nqm * D;
-        T* dh = delta + ((int64_t)b * Hq + hq) * nqm * (int64_t)Np;
         for (int m0 = 0; m0 < nqm_live && alive; m0 += 128, ++iter) {
-            // A tile: 128 query-block means, same swizzled layout
-            for (int idx = t; idx < 128 * (D / 8); idx += 256) {
-                const int r = idx / (D / 8), chunk = idx % (D / 8);
-                uint4 val = make_uint4(0, 0, 0, 0);
-                if (m0 + r < nqm_live) val = __ldg(reinterpret_cast<const uint4*>(qmh + (int64_t)(m0 + r) * D + chunk * 8));
-                *reinterpret_cast<uint4*>(sgen + oA + (chunk >> 3) * 16384 + r * 128 + (((chunk & 7) ^ (r & 7)) << 4)) = val;
-            }
-            fence_proxy_async_smem();
-            tc_fence_before();
+            // A tile: 128 query-block means, fetched by the copy engine in the 128-byte swizzle the MMA reads.  Rows beyond
+            // the tensor's nqm arrive as zeros; rows of a shorter sequence of a packed batch only feed accumulator rows
+            // that nobody reads.
+            fence_proxy_async_smem();       // this thread's stores (the k' tile; the previous epilogue's staging) before the engine touches the tiles
             __syncthreads();
+            if (t == 0) {
+                mbar_expect_tx(bar_a, SUB * 16384);
+#pragma unroll
+                for (int sub = 0; sub < SUB; ++sub)
+                    tma_load_3d(sbase + oA + sub * 16384, &tm_qm, bar_a, sub * 128, m0, b * Hq + hq);
+            }
+            alive = mbar_wait(bar_a, iter & 1, abort_flag, status, kWaitDeltaA);
+            tc_fence_before();
+            alive = __syncthreads_and(alive ? 1 : 0) != 0;
+            if (!alive) break;
             if (t == 0) {
                 tc_fence_after();
 #pragma unroll
@@ -494,12 +501,12 @@ __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
             alive = __syncthreads_and(alive ? 1 : 0) != 0;
             if (!alive) break;
             tc_fence_after();
-            // epilogue: thread = query block (row) of the accumulator, 64 keys of its row = 128 contiguous bytes of delta_s
-            const uint32_t acc = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + chalf * 64;
-            if constexpr (D == 128) {
-                // The warp's 32 rows x 128 bytes go through a swizzled tile in shared memory (the A tile is free once
-                // the MMAs have completed), so that eight lanes store one whole 128-byte line.
-                uint8_t* stg = sgen + oA + warp * 4096;
+            // epilogue: thread = query block (row) of the accumulator, 64 keys of its row = 128 contiguous bytes of delta_s.
+            // The warp's 32 rows x 128 bytes are staged in shared memory in the 128-byte swizzle (at D = 128 in the A tile,
+            // which is free once the MMAs have completed) and leave as one TMA tile store; the engine clips rows beyond nqm.
+            {
+                const uint32_t acc = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + chalf * 64;
+                uint8_t* stg = sgen + oStg + warp * 4096;
 #pragma unroll
                 for (int cc = 0; cc < 2; ++cc) {
                     float v[32];
@@ -514,35 +521,14 @@ __global__ void __launch_bounds__(256, 3) quant_k_delta_kernel(
                             make_uint4(p4[0], p4[1], p4[2], p4[3]);
                     }
                 }
+                fence_proxy_async_smem();
                 __syncwarp();
-                const int ch = lane & 7;
-#pragma unroll
-                for (int k2 = 0; k2 < 8; ++k2) {
-                    const int row = k2 * 4 + (lane >> 3);
-                    const uint4 val = *reinterpret_cast<const uint4*>(stg + row * 128 + ((ch ^ (row & 7)) << 4));
-                    const int qb = m0 + quarter * 32 + row;
-                    if (qb < nqm_live) *reinterpret_cast<uint4*>(dh + (int64_t)qb * Np + row0 + chalf * 64 + ch * 8) = val;
+                if (lane == 0 && m0 + quarter * 32 < nqm) {
+                    tma_store_3d(&tm_delta, sbase + oStg + warp * 4096, (row0 + chalf * 64) * 2, m0 + quarter * 32, b * Hq + hq);
+                    bulk_commit_group();
+                    bulk_wait_group_read0();      // the engine has read the staging tile: it may be written again
                 }
                 __syncwarp();
-            } else {
-                // D = 64 (its A tile is too small to stage eight warps): every lane stores whole 32-byte sectors
-                const int qb = m0 + quarter * 32 + lane;
-#pragma unroll
-                for (int cc = 0; cc < 2; ++cc) {
-                    float v[32];
-                    tmem_ld32(acc + cc * 32, v);
-                    tc_wait_ld();
-                    if (qb < nqm_live) {
-                        T* drow = dh + (int64_t)qb * Np + row0 + chalf * 64 + cc * 32;
-#pragma unroll
-                        for (int i = 0; i < 2; ++i) {
-                            uint32_t p8[8];
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) p8[e] = Num<T>::pack2(v[16 * i + 2 * e], v[16 * i + 2 * e + 1]);
-                            st_global_256(drow + 16 * i, p8);
-                        }
-                    }
-                }
             }
             tc_fence_before();
             __syncthreads();      // the accumulator and the A tile are free again
@@ -658,11 +644,16 @@ static cudaError_t launch_prepass_t(const PrepassArgs& a, cudaStream_t st) {
         quant_rows_kernel<T, D, kModeQGlobalMean><<<dim3(a.Nq_p / kBlock, BHq), 256, smem_q, st>>>(
             q, a.qs[0], a.qs[1], a.qs[2], a.Hq, a.Nq, a.Nq_p, qm, nullptr, a.q_codes, a.q_sf, km, a.Hq / a.Hkv, a.qkm);
     }
-    const size_t smem_k = 2 * (D / 64) * 16384 + D * 4 + (D / 64) * 512 + 64 + 1024;
+    const size_t smem_k = 2 * (D / 64) * 16384 + D * 4 + (D / 64) * 512 + 64 + 1024 + (D == 64 ? 1024 + 32768 : 0);
     cudaError_t e = cudaFuncSetAttribute(quant_k_delta_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_k);
     if (e != cudaSuccess) return e;
+    // tensor maps for the K kernel: the Q means [B*Hq][nqm][D] and delta_s [B*Hq][nqm][Nk_p] as byte tensors
+    alignas(64) CUtensorMap tm_qm, tm_delta;
+    if (encode_tiled_bytes(&tm_qm, qm, (uint64_t)D * 2, (uint64_t)a.nqm, (uint64_t)a.B * a.Hq, 128, 128, 3) != 0 ||
+        encode_tiled_bytes(&tm_delta, delta, (uint64_t)a.Nk_p * 2, (uint64_t)a.nqm, (uint64_t)a.B * a.Hq, 128, 32, 3) != 0)
+        return cudaErrorInvalidValue;
     quant_k_delta_kernel<T, D><<<dim3(a.Nk_p / kBlock, BHkv), 256, smem_k, st>>>(
-        k, a.ks[0], a.ks[1], a.ks[2], a.Hkv, a.Nk, a.Nk_p, km, a.k_codes, a.k_sf, qm, delta, a.Hq, a.nqm, a.status, a.cu_q);
+        k, a.ks[0], a.ks[1], a.ks[2], a.Hkv, a.Nk, a.Nk_p, km, a.k_codes, a.k_sf, a.Hq, a.nqm, a.status, a.cu_q, tm_qm, tm_delta);
 
     const size_t smem_v = ((kBlock * (D + 2) * sizeof(T) + 15) / 16) * 16 + D * 72 + 1024;
     e = cudaFuncSetAttribute(quant_vt_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_v);
