@@ -142,6 +142,16 @@ SAGE3_API int sage3_fwd_varlen(const Sage3Desc* desc, const int32_t* cu_seqlens_
                                const void* k, const void* v, void* out, float* lse, void* ws, void* stream);
 
 /*
+ * Column means from partial column sums: mean_out[r][d] (dtype, [rows][D]) = the sum over c = 0 .. chunks - 1, in that
+ * order, of part[r][c][d] (fp32, [rows][chunks][D]), times 1 / count, rounded once -- the second half of the K-mean stage
+ * (api.py:84) on its own.  Context-parallel callers gather the 512-row partial sums that sage3_prepass leaves in the
+ * `kpart` region of every rank's workspace, shard after shard, and obtain the K mean of the whole sequence exactly as a
+ * single call forms it (then passed to sage3_prepass_kmean).
+ */
+SAGE3_API int sage3_mean_from_partial_sums(const float* part, int32_t rows, int32_t chunks, int32_t D, int32_t dtype, int64_t count,
+                                           void* mean_out, void* stream);
+
+/*
  * sage3_prepass with the K mean supplied by the caller: `km` is a device array dtype[B][Hkv][D] that is used instead of
  * the mean over this call's Nk tokens.  For context-parallel callers whose K is one shard of a longer sequence: they
  * pass the mean over all shards, so every shard is smoothed exactly as the whole sequence would be (api.py:84 takes

@@ -100,6 +100,8 @@ def lib() -> C.CDLL:
     l.sage3_fwd.argtypes = [P(Sage3Desc), V, V, V, V, V, V, V]
     l.sage3_fwd_varlen.restype = C.c_int
     l.sage3_fwd_varlen.argtypes = [P(Sage3Desc), V, V, V, V, V, V, V, V, V]
+    l.sage3_mean_from_partial_sums.restype = C.c_int
+    l.sage3_mean_from_partial_sums.argtypes = [V, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, V, V]
     l.sage3_selftest_wait_timeout.restype = C.c_int
     l.sage3_selftest_wait_timeout.argtypes = [V, V]
     l.sage3_slab_copy.restype = C.c_int
@@ -117,7 +119,7 @@ def lib() -> C.CDLL:
 EXPORTED = ["sage3_version", "sage3_strerror", "sage3_workspace_layout", "sage3_workspace_bytes", "sage3_prepass",
             "sage3_attn_fwd", "sage3_fwd", "sage3_check_status", "sage3_kmean_noalloc", "sage3_selftest_wait_timeout", "sage3_slab_copy", "sage3_merge_partial",
             "sage3_prepass_kmean", "sage3_prepass_parts", "sage3_attn_fwd_parts", "sage3_attn_fwd_carry", "sage3_shared_alloc", "sage3_shared_open",
-            "sage3_shared_close", "sage3_shared_free", "sage3_fwd_varlen"]
+            "sage3_shared_close", "sage3_shared_free", "sage3_fwd_varlen", "sage3_mean_from_partial_sums"]
 
 
 def check(code: int, where: str) -> None:

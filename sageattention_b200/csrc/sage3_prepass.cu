@@ -714,6 +714,27 @@ cudaError_t launch_kmean_t(const Sage3Desc* d, const void* k, void* km, float* s
 
 }  // namespace
 
+// Column means from partial column sums: mean[r][d] = round(dtype, (sum over c, in order, of part[r][c][d]) * (1 / count)).
+// The second half of the K-mean stage on its own, for callers that gather the partial sums of several token shards
+// (one 512-row chunk after the other, shard after shard) and need the mean the single call forms, bit for bit.
+extern "C" SAGE3_API int sage3_mean_from_partial_sums(const float* part, int32_t rows, int32_t chunks, int32_t D, int32_t dtype,
+                                                      int64_t count, void* mean_out, void* stream) {
+    if (!part || !mean_out) return SAGE3_E_NULL;
+    if (rows <= 0 || chunks <= 0 || count <= 0 || (D != 64 && D != 128)) return SAGE3_E_SHAPE;
+    if (dtype != SAGE3_FP16 && dtype != SAGE3_BF16) return SAGE3_E_DTYPE;
+    if ((reinterpret_cast<uintptr_t>(part) % 4) != 0 || (reinterpret_cast<uintptr_t>(mean_out) % 2) != 0) return SAGE3_E_ALIGN;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const float inv = 1.0f / (float)count;
+    if (dtype == SAGE3_BF16) {
+        if (D == 128) sage3::colmean_finalize_kernel<__nv_bfloat16, 128><<<rows, 128, 0, st>>>(part, chunks, inv, static_cast<__nv_bfloat16*>(mean_out), nullptr, 1, 0);
+        else sage3::colmean_finalize_kernel<__nv_bfloat16, 64><<<rows, 64, 0, st>>>(part, chunks, inv, static_cast<__nv_bfloat16*>(mean_out), nullptr, 1, 0);
+    } else {
+        if (D == 128) sage3::colmean_finalize_kernel<__half, 128><<<rows, 128, 0, st>>>(part, chunks, inv, static_cast<__half*>(mean_out), nullptr, 1, 0);
+        else sage3::colmean_finalize_kernel<__half, 64><<<rows, 64, 0, st>>>(part, chunks, inv, static_cast<__half*>(mean_out), nullptr, 1, 0);
+    }
+    return cudaGetLastError() == cudaSuccess ? SAGE3_OK : SAGE3_E_CUDA;
+}
+
 extern "C" SAGE3_API int sage3_kmean_noalloc(const Sage3Desc* desc, const void* k, void* km_out, void* stream) {
     if (!desc || !k || !km_out) return SAGE3_E_NULL;
     if (desc->B <= 0 || desc->Hkv <= 0 || desc->Nk <= 0 || (desc->D != 64 && desc->D != 128)) return SAGE3_E_SHAPE;

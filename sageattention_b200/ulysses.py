@@ -304,12 +304,11 @@ def context_parallel_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
     kpart = prob.ws.buf[lay.kpart: lay.kpart + B * Hkv * chunks * D * 4].view(torch.float32).view(B * Hkv, chunks, D)
     allpart = torch.empty(world, B * Hkv, chunks, D, dtype=torch.float32, device=dev)
     dist.all_gather_into_tensor(allpart, kpart.contiguous(), group=group)
-    acc = torch.zeros(B * Hkv, D, dtype=torch.float32, device=dev)
-    for r_ in range(world):
-        for c_ in range(chunks):
-            acc = acc + allpart[r_, :, c_]
-    inv = torch.tensor(1.0, dtype=torch.float32, device=dev) / torch.tensor(float(world * n), dtype=torch.float32, device=dev)
-    km = (acc * inv).to(dt).contiguous()
+    ordered = allpart.permute(1, 0, 2, 3).contiguous()         # [B*Hkv][shard][chunk][D]: the single call's chunk order
+    km = torch.empty(B, Hkv, D, dtype=dt, device=dev)
+    with torch.cuda.device(dev):
+        _cabi.check(lib.sage3_mean_from_partial_sums(ordered.data_ptr(), B * Hkv, world * chunks, D, prob.desc.dtype, world * n,
+                                                     km.data_ptr(), stream), "sage3_mean_from_partial_sums")
 
     o_acc = torch.empty(B, Hq, n, D, dtype=torch.float32, device=dev)
     m_acc = torch.empty(B, Hq, n, dtype=torch.float32, device=dev)
