@@ -49,6 +49,9 @@ class Workspace:
         return self.buf[off: off + nbytes] if nbytes is not None else self.buf[off:]
 
 
+CACHED_WORKSPACE = object()      # `workspace=` value: take the per-(device, stream) buffer the functional entry points share
+
+
 class Sage3Problem:
     """Shapes, strides and workspace of one call; reusable while shapes, strides and dtype stay the same."""
 
@@ -114,7 +117,9 @@ class Sage3Problem:
 
         lay = _cabi.Sage3Workspace()
         _cabi.check(_cabi.lib().sage3_workspace_layout(C.byref(d), C.byref(lay)), "sage3_workspace_layout")
-        if workspace is None:
+        if workspace is CACHED_WORKSPACE:
+            workspace = _shared_buffer(q.device, lay.total_bytes + 256)
+        elif workspace is None:
             workspace = torch.empty(lay.total_bytes + 256, dtype=torch.uint8, device=q.device)
         elif workspace.numel() < lay.total_bytes + 256 or workspace.dtype != torch.uint8 or workspace.device != q.device:
             raise ValueError(f"workspace must be a uint8 CUDA tensor of at least {lay.total_bytes + 256} bytes")
@@ -215,11 +220,38 @@ def sageattn3(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: 
         if return_lse:
             return torch.ops.sageattention_b200.fwd_lse(q, k, v, tensor_layout, bool(is_causal), scale_f, scale_t, bool(per_block_mean))
         return torch.ops.sageattention_b200.fwd(q, k, v, tensor_layout, bool(is_causal), scale_f, scale_t, bool(per_block_mean))
-    if workspace is None and q.is_cuda:
-        workspace = _cached_workspace(q, k, tensor_layout, per_block_mean)
-    prob = Sage3Problem(q, k, v, tensor_layout, is_causal, sm_scale, per_block_mean, workspace=workspace,
-                        return_lse=return_lse)
+    # Repeated calls with one signature (the common case: every layer of a model) reuse the validated descriptor: what is
+    # left per call is two allocations and one call into the library.
+    plan_key = None
+    if workspace is None and not isinstance(sm_scale, torch.Tensor) and q.is_cuda:
+        plan_key = (q.device.index, q.dtype, k.dtype, v.dtype, tuple(q.shape), tuple(k.shape), tuple(v.shape), q.stride(), k.stride(),
+                    v.stride(), tensor_layout, bool(is_causal), sm_scale, bool(per_block_mean))
+        plan = _PLANS.get(plan_key)
+        if plan is not None:
+            desc, total_bytes, lse_shape = plan
+            dev = q.device
+            out = torch.empty(q.shape, dtype=q.dtype, device=dev)
+            lse = torch.empty(lse_shape, dtype=torch.float32, device=dev) if return_lse else None
+            buf = _shared_buffer(dev, total_bytes + 256)
+            ws_ptr = buf.data_ptr()
+            ws_ptr += (-ws_ptr) % 256
+            args = (C.byref(desc), q.data_ptr(), k.data_ptr(), v.data_ptr(), ws_ptr, out.data_ptr(),
+                    None if lse is None else lse.data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+            if torch.cuda.current_device() == dev.index:
+                rc = _cabi.lib().sage3_fwd(*args)
+            else:
+                with torch.cuda.device(dev):
+                    rc = _cabi.lib().sage3_fwd(*args)
+            _cabi.check(rc, "sage3_fwd")
+            return (out, lse) if return_lse else out
+    prob = Sage3Problem(q, k, v, tensor_layout, is_causal, sm_scale, per_block_mean,
+                        workspace=CACHED_WORKSPACE if workspace is None else workspace, return_lse=return_lse)
     out = prob.run()
+    if plan_key is not None and prob.q is q and prob.k is k and prob.v is v:      # no copies were needed: the signature is reusable
+        if len(_PLANS) >= 256:
+            _PLANS.clear()
+        hd, nd = (1, 2) if tensor_layout == "HND" else (2, 1)
+        _PLANS[plan_key] = (prob.desc, prob.ws.layout.total_bytes, (q.shape[0], q.shape[hd], q.shape[nd]))
     return (out, prob.lse) if return_lse else out
 
 
@@ -230,27 +262,23 @@ def sageattn3(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: 
 # stream run in order, so they may share it; calls on different streams get different buffers.  (Allocating 3.4 GB anew
 # on every call of the benchmark shape costs more than the pre-pass.)  Sage3Problem users manage their own.
 _WORKSPACES: dict = {}
+_PLANS: dict = {}            # signature of a sageattn3 call -> (validated descriptor, workspace bytes, LSE shape)
 
 
-def _cached_workspace(q: torch.Tensor, k: torch.Tensor, tensor_layout: str, per_block_mean: bool) -> torch.Tensor:
-    hd, nd = (1, 2) if tensor_layout == "HND" else (2, 1)
-    d = _cabi.Sage3Desc()
-    d.B, d.Hq, d.Hkv, d.Nq, d.Nk, d.D = q.shape[0], q.shape[hd], k.shape[hd], q.shape[nd], k.shape[nd], q.shape[3]
-    d.dtype = _DTYPES.get(q.dtype, _cabi.SAGE3_BF16)
-    d.per_block_mean = int(bool(per_block_mean))
-    need = _cabi.lib().sage3_workspace_bytes(C.byref(d))      # 0 for an invalid shape: Sage3Problem reports it properly
-    key = (q.device.index, torch.cuda.current_stream(q.device).cuda_stream)
+def _shared_buffer(device: torch.device, nbytes: int) -> torch.Tensor:
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
     buf = _WORKSPACES.get(key)
-    if buf is None or buf.numel() < need + 256:
+    if buf is None or buf.numel() < nbytes:
         _WORKSPACES.pop(key, None)
-        buf = torch.empty(need + 256, dtype=torch.uint8, device=q.device)
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
         _WORKSPACES[key] = buf
     return buf
 
 
 def release_workspaces() -> None:
-    """Drops the workspaces that sageattn3 / sageattn / sageattn_varlen keep between calls."""
+    """Drops the workspaces (and call signatures) that sageattn3 / sageattn / sageattn_varlen keep between calls."""
     _WORKSPACES.clear()
+    _PLANS.clear()
 
 
 # ------------------------------------------------------------------------------------------------------
@@ -260,8 +288,7 @@ def release_workspaces() -> None:
 # ------------------------------------------------------------------------------------------------------
 def _op_impl(q, k, v, tensor_layout, is_causal, sm_scale, sm_scale_per_head, per_block_mean, return_lse):
     scale = sm_scale_per_head if sm_scale_per_head is not None else sm_scale
-    prob = Sage3Problem(q, k, v, tensor_layout, is_causal, scale, per_block_mean,
-                        workspace=_cached_workspace(q, k, tensor_layout, per_block_mean), return_lse=return_lse)
+    prob = Sage3Problem(q, k, v, tensor_layout, is_causal, scale, per_block_mean, workspace=CACHED_WORKSPACE, return_lse=return_lse)
     out = prob.run()
     return (out, prob.lse) if return_lse else out
 
@@ -387,12 +414,7 @@ def _varlen_impl(q, k, v, cq, ck, max_seqlen_q, max_seqlen_k, is_causal, sm_scal
     need = _cabi.lib().sage3_workspace_bytes(C.byref(d))
     if need == 0:
         raise ValueError("sageattn_varlen: shape not supported (see sage3_workspace_layout)")
-    key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
-    buf = _WORKSPACES.get(key)
-    if buf is None or buf.numel() < need + 256:
-        _WORKSPACES.pop(key, None)
-        buf = torch.empty(need + 256, dtype=torch.uint8, device=dev)
-        _WORKSPACES[key] = buf
+    buf = _shared_buffer(dev, need + 256)
     shift = (-buf.data_ptr()) % 256
     with torch.cuda.device(dev):
         _cabi.check(_cabi.lib().sage3_fwd_varlen(C.byref(d), cq.data_ptr(), ck.data_ptr(), qc.data_ptr(), kc.data_ptr(),
